@@ -108,24 +108,41 @@ class CMoeSpec(ctypes.Structure):
 
 
 class CMixerSpec(ctypes.Structure):
-    """``cake_b200_mixer_spec`` (include/cake_b200.h)."""
-    _fields_ = [("kind", c_int), ("heads", c_int), ("dim", c_int), ("vdim", c_int), ("rot_dim", c_int), ("kv_rank", c_int), ("scale", c_float),
-                ("rot", CRotarySpec), ("decay", POINTER(c_float)), ("state", c_int), ("groups", c_int), ("conv", c_int), ("norm_groups", c_int),
-                ("moe", CMoeSpec)]
+    """``cake_b200_mixer_spec`` (include/cake_b200.h); ``side`` points to the spec of a second mixer beside this one."""
+
+
+CMixerSpec._fields_ = [("kind", c_int), ("heads", c_int), ("dim", c_int), ("vdim", c_int), ("rot_dim", c_int), ("kv_rank", c_int), ("scale", c_float),
+                       ("rot", CRotarySpec), ("decay", POINTER(c_float)), ("state", c_int), ("groups", c_int), ("conv", c_int), ("norm_groups", c_int),
+                       ("moe", CMoeSpec),
+                       ("kv_heads", c_int), ("bias_rows", c_int), ("bias_max", c_float), ("gate_cap", c_float), ("norm_offset", c_float),
+                       ("canon_taps", c_int), ("dense_ff", c_int), ("dense_act", c_int), ("dense_limit", c_float), ("side", POINTER(CMixerSpec))]
 
 
 MIXER_TENSOR_FIELDS = ("norm1", "norm2", "q", "k", "v", "g", "o", "dkv", "dkv_norm", "uk", "uv", "in", "conv", "conv_b", "dt_bias", "a_log", "d",
-                       "norm", "router", "correction", "e_gate", "e_up", "e_down", "s_gate", "s_up", "s_down", "s_sg")
+                       "norm", "router", "correction", "e_gate", "e_up", "e_down", "s_gate", "s_up", "s_down", "s_sg",
+                       "post1", "post2", "canon", "q_conv", "k_conv", "v_conv", "beta", "a_proj", "q_b", "k_b", "v_b", "o_b", "rel", "talk",
+                       "i_proj", "i_b", "f_proj", "f_b", "ff_gate", "ff_up", "ff_down", "branch_norm")
 
 
 class CMixerTensors(ctypes.Structure):
-    """``cake_b200_mixer_tensors`` (include/cake_b200.h); e_gate / e_up / e_down are arrays of ``experts`` pointers."""
-    _fields_ = [(n, POINTER(_VP) if n.startswith("e_") else _VP) for n in MIXER_TENSOR_FIELDS]
+    """``cake_b200_mixer_tensors`` (include/cake_b200.h); e_gate / e_up / e_down are arrays of ``experts`` pointers, ``side`` the
+    tensors of a second mixer beside this one."""
+
+
+CMixerTensors._fields_ = [(n, POINTER(_VP) if n.startswith("e_") else _VP) for n in MIXER_TENSOR_FIELDS] + [("side", POINTER(CMixerTensors))]
+
+
+class CEmbedTables(ctypes.Structure):
+    """``cake_b200_embed_tables`` (include/cake_b200.h)."""
+    _fields_ = [("bigram", _VP), ("bigram_rows", c_int), ("mul_prev", c_int), ("mul_cur", c_int), ("pos", _VP), ("pos_rows", c_int),
+                ("final_norm_offset", c_float)]
 
 
 SYMBOLS += [
     ("cake_b200_block_load_mixer", _I, [_VP, _I, POINTER(CMixerSpec), POINTER(CMixerTensors), POINTER(_VP)]),
     ("cake_b200_stream_inject", _I, [_VP, _VP, _VP, _VP, _I, _I]),
+    ("cake_b200_head_load_tables", _I, [_VP, POINTER(CEmbedTables)]),
+    ("cake_b200_embed_at", _I, [_VP, _VP, POINTER(c_uint32), _I, _I, _I, _VP]),
 ]
 
 

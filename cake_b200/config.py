@@ -86,7 +86,7 @@ class MoeSpec:
     act: int = 0
 
 
-MIXER_KINDS = {"latent_attention": 1, "retention": 2, "mamba2": 3}
+MIXER_KINDS = {"latent_attention": 1, "retention": 2, "mamba2": 3, "delta": 4, "talking_attention": 5, "matrix_memory": 6}
 
 
 @dataclass
@@ -107,10 +107,28 @@ class MixerSpec:
     conv: int = 1
     norm_groups: int = 1
     moe: Optional[MoeSpec] = None
+    # delta (gated delta rule), talking_attention (softmax attention with a bucketed distance bias whose heads' weights are mixed
+    # after the softmax) and matrix_memory (a matrix memory with exponential gates), and the block structure switches they come
+    # with: gains stored as offsets, post norms, a convolution in front of the mixer, a side mixer, a dense feed-forward
+    kv_heads: int = 0        # delta, talking_attention (0 = heads)
+    bias_rows: int = 0       # talking_attention: rows of the distance-bias table (read from the tensor's shape at load)
+    bias_max: float = 0.0
+    gate_cap: float = 0.0    # matrix_memory
+    norm_offset: float = 0.0
+    post_norms: bool = False
+    canon_taps: int = 0
+    dense_ff: int = 0
+    dense_act: int = 0       # 0 silu, 1 tanh-gelu, 2 clamped (min(g, limit) sigmoid(1.702 g) (clamp(u) + 1))
+    dense_limit: float = 0.0
+    side: Optional["MixerSpec"] = None   # a second mixer beside this one, reading the same input
 
     @property
     def inner(self) -> int:
         return self.heads * self.vdim
+
+    @property
+    def n_kv(self) -> int:
+        return self.kv_heads or self.heads
 
 
 @dataclass
@@ -145,6 +163,10 @@ class Config:
     layers: list = field(default_factory=list)  # layer-list models: one LayerSpec per layer (sizes differ between layers)
     logit_softcap: float = 0.0        # logits <- cap * tanh(logits / cap) after the head (0 = none)
     loop: Optional[dict] = None       # mixer-list models: {"start", "stop", "times"}: layers start..stop-1 run `times` times in a row
+    loop_injects: bool = True         # the stream receives a per-pass vector (and the embedding output again) in front of every pass
+    pair_embedding: Optional[dict] = None  # {"buckets", "mul_prev", "mul_cur"}: a hashed (previous, current) token embedding is added
+    learned_positions: int = 0        # > 0: a learned vector per position is added to the embedding (rows of the table)
+    final_norm_offset: float = 0.0    # the final norm's gain is stored as an offset from this number
 
     def layer_variant(self, i: int, max_seq: Optional[int] = None) -> dict:
         """Norm placement and attention mode of layer ``i``, as the reference's per-architecture block.rs sets them up:
@@ -176,7 +198,7 @@ class Config:
     @property
     def layer_list(self) -> bool:
         """The checkpoint's config lists its layers one by one; such models keep an fp32 residual stream."""
-        return self.block_kind in ("nigenex", "setodra")
+        return self.block_kind in ("nigenex", "setodra", "nuvarax")
 
     @property
     def scalar_final_norm(self) -> bool:
@@ -198,7 +220,7 @@ class Config:
     def head_tensor_names(self):
         """(embedding, final norm, lm_head or None when tied) as the checkpoint names them (text_model.rs:159-193)."""
         if self.layer_list:
-            return "embed", "final.norm", "head"
+            return "embed", "final.norm", None if self.tie_word_embeddings else "head"
         p = self.model_prefix
         return f"{p}.embed_tokens.weight", f"{p}.norm.weight", None if self.tie_word_embeddings else "lm_head.weight"
 
@@ -314,6 +336,71 @@ class Config:
                      embed_scale=float((d.get("embedding") or {}).get("scale") or 0.0) or None, loop=loop)
         return cfg
 
+    @staticmethod
+    def _from_nuvarax(d: dict) -> "Config":
+        """Nuvarax ``config.json``: ``width``, ``vocab``, ``norm.eps``, ``max_positions``, ``embedding.{scale, bigram.{buckets,
+        mul_prev, mul_cur}}``, ``canon.taps``, an optional ``loop`` and ``layers``, whose entries give ``type`` (``delta``: a gated
+        delta rule mixer; ``parallel``: attention with mixed heads (``mixer.left``) beside a matrix memory (``mixer.right``)), the
+        mixer's sizes and the dense feed-forward (``mlp``: kind ``dense`` with ``ff`` and ``limit``, or null).  Every norm's gain
+        is stored as an offset from one; the output projection is the embedding table."""
+        taps = int((d.get("canon") or {}).get("taps") or 0)
+        specs = []
+        for i, L in enumerate(d["layers"]):
+            kind, m = L.get("type"), L["mixer"]
+            if kind == "delta":
+                sp = MixerSpec(type="delta", heads=int(m["heads"]), kv_heads=int(m.get("kv_heads") or m["heads"]), dim=int(m["dim"]),
+                               vdim=int(m["vdim"]), conv=int(m.get("conv") or 1))
+            elif kind == "parallel":
+                a, b = m["left"], m["right"]
+                sp = MixerSpec(type="talking_attention", heads=int(a["heads"]), kv_heads=int(a.get("kv_heads") or a["heads"]), dim=int(a["dim"]),
+                               vdim=int(a["vdim"]), scale=float(a["scale"]), bias_max=float(a.get("bias_max") or 0.0),
+                               side=MixerSpec(type="matrix_memory", heads=int(b["heads"]), dim=int(b["dim"]), vdim=int(b["vdim"]),
+                                              gate_cap=float(b["gate_cap"])))
+            else:
+                raise ValueError(f"layer {i}: mixer type {kind!r} is not part of this design")
+            if sp.heads % sp.n_kv:
+                raise ValueError(f"layer {i}: {sp.heads} heads over {sp.n_kv} key heads")
+            mlp = L.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") != "dense":
+                    raise ValueError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} is not part of this design")
+                sp.dense_ff, sp.dense_act, sp.dense_limit = int(mlp["ff"]), 2, float(mlp["limit"])
+            sp.norm_offset, sp.post_norms, sp.canon_taps = 1.0, True, taps
+            specs.append(sp)
+        if not specs:
+            raise ValueError("config lists no layers")
+        loop = d.get("loop") or None
+        if loop and not (0 <= int(loop["start"]) < int(loop["stop"]) <= len(specs) and int(loop["times"]) >= 1):
+            raise ValueError(f"bad loop {loop}")
+        emb = d.get("embedding") or {}
+        bg = emb.get("bigram") or None
+        npos = int(d.get("max_positions") or 0)
+        return Config(hidden_size=int(d["width"]), intermediate_size=0, vocab_size=int(d["vocab"]), num_hidden_layers=len(specs),
+                      num_attention_heads=specs[0].heads, num_key_value_heads=specs[0].n_kv, rms_norm_eps=float(d["norm"]["eps"]),
+                      head_dim=specs[0].vdim, max_seq_len=npos or 4096, block_kind="nuvarax", layers=specs, model_prefix="",
+                      embed_scale=float(emb.get("scale") or 0.0) or None, loop=loop, loop_injects=False, tie_word_embeddings=True,
+                      pair_embedding={k: int(bg[k]) for k in ("buckets", "mul_prev", "mul_cur")} if bg else None,
+                      learned_positions=npos, final_norm_offset=1.0)
+
+    def to_nuvarax(self) -> dict:
+        """The ``config.json`` of a Nuvarax Config (inverse of ``_from_nuvarax``)."""
+        layers = []
+        for s in self.layers:
+            if s.type == "delta":
+                kind, m = "delta", {"heads": s.heads, "kv_heads": s.n_kv, "dim": s.dim, "vdim": s.vdim, "conv": s.conv}
+            else:
+                r = s.side
+                kind, m = "parallel", {"left": {"heads": s.heads, "kv_heads": s.n_kv, "dim": s.dim, "vdim": s.vdim, "scale": s.scale, "bias_max": s.bias_max},
+                                       "right": {"heads": r.heads, "dim": r.dim, "vdim": r.vdim, "gate_cap": r.gate_cap}}
+            layers.append({"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": s.dense_ff, "limit": s.dense_limit} if s.dense_ff else None})
+        d = {"architecture": "Nuvarax", "width": self.hidden_size, "vocab": self.vocab_size, "norm": {"eps": self.rms_norm_eps},
+             "max_positions": self.learned_positions, "canon": {"taps": self.layers[0].canon_taps},
+             "embedding": {"scale": self.embed_scale if self.embed_scale else 1.0, "bigram": dict(self.pair_embedding) if self.pair_embedding else None},
+             "layers": layers}
+        if self.loop:
+            d["loop"] = dict(self.loop)
+        return d
+
     def to_setodra(self) -> dict:
         """The ``config.json`` of a mixer-list Config (inverse of ``_from_setodra``)."""
         layers = []
@@ -349,6 +436,8 @@ class Config:
             return Config._from_nigenex(d)
         if d.get("architecture") == "Setodra":
             return Config._from_setodra(d)
+        if d.get("architecture") == "Nuvarax":
+            return Config._from_nuvarax(d)
         arch = Config.detect_arch(d)
         if arch in Config._OTHER_BLOCKS:
             raise ValueError(f"architecture {arch!r} is outside the block-forward path built here")
@@ -435,6 +524,8 @@ class Config:
             return self.to_nigenex()
         if self.block_kind == "setodra":
             return self.to_setodra()
+        if self.block_kind == "nuvarax":
+            return self.to_nuvarax()
         d = dict(
             architectures=[arch], hidden_size=self.hidden_size, intermediate_size=self.intermediate_size,
             vocab_size=self.vocab_size, num_hidden_layers=self.num_hidden_layers,

@@ -151,6 +151,10 @@ struct cake_b200_ctx {
   size_t mx_ws_cap = 0;
   void *inject_vec[64] = {};
   const void *inject_src[64] = {};
+  // cake_b200_head_load_tables: hashed pair embedding, learned position vectors, the final norm's gain offset
+  void *bigram = nullptr, *pos_tab = nullptr;
+  int bigram_rows = 0, mul_prev = 0, mul_cur = 0, pos_rows = 0;
+  float final_norm_offset = 0.f;
   // comm
   ncclComm_t comm = nullptr;
   int rank = 0, world = 1;
@@ -210,6 +214,16 @@ struct cake_b200_block {
   void *m_router = nullptr, *m_corr = nullptr, *m_eg = nullptr, *m_ed = nullptr;
   float *m_cos = nullptr, *m_sin = nullptr, *m_decay = nullptr;
   int m_rope_rows = 0;
+  // the block structure switches of cake_b200_mixer_spec (norm_offset, post norms, canon_taps, side, dense_ff) and the delta /
+  // talking-attention / matrix-memory mixers: `ext` blocks run enqueue_ext_layer.  A side mixer's own tensors live in a nested
+  // block; its projections are rows of this block's w_in.  pc[]: the column of each projection part in the step's `proj`.
+  bool ext = false;
+  cake_b200_block *side = nullptr;
+  void *post1 = nullptr, *post2 = nullptr, *canon = nullptr, *b_in = nullptr;
+  void *m_ob = nullptr, *m_talk = nullptr, *m_branch = nullptr, *m_ib = nullptr, *m_fb = nullptr;
+  float *m_bias = nullptr;   // [m_bias_len, heads] fp32: the distance bias by distance
+  int m_bias_len = 0;
+  int pc[6] = {0, 0, 0, 0, 0, 0};
   bool variant() const { return !ln1 || !ln2 || pan || pfn || window >= 0 || !use_rope || ctx->cfg.pre_reshape_qk_norm; }
 };
 
@@ -229,6 +243,13 @@ struct cake_b200_cache {
   // mixer-list blocks: recurrent state [batch, heads, dk, dv] fp32 and the convolution's last taps - 1 inputs, per block_idx
   std::vector<float *> rec_state;
   std::vector<void *> conv_hist;
+  // ext blocks: k / v / rec_state / conv_hist / rec_aux have a second entry per block_idx (index n_layers + block_idx) for a
+  // side mixer; rec_aux: the normaliser and running maximum of a matrix memory [batch, heads, dk + 1] fp32; canon_hist: the
+  // last canon_taps - 1 normed inputs of the block [batch, taps - 1, hidden] fp32
+  std::vector<float *> rec_aux, canon_hist;
+  // cake_b200_embed_at: the last token of every batch row and the position the embedding has reached
+  std::vector<uint32_t> last_tok;
+  int embed_len = 0;
 };
 
 template <typename U> struct TypeTag { typedef U type; };
@@ -550,6 +571,8 @@ extern "C" void cake_b200_ctx_destroy(cake_b200_ctx *c) {
                   c->samp_p, c->samp_noise, c->x0, c->sp_h, c->sp_hs, c->sp_in, c->sp_a, c->sp_hn, c->sp_logits, c->sp_rows_idx, c->mx_ws};
   for (void *b : bufs)
     if (b) cudaFree(b);
+  if (c->bigram) cudaFree(c->bigram);
+  if (c->pos_tab) cudaFree(c->pos_tab);
   for (void *b : c->inject_vec)
     if (b) cudaFree(b);
   if (c->lm_head && c->lm_head != c->embed) cudaFree(c->lm_head);
@@ -735,9 +758,11 @@ extern "C" void cake_b200_block_free(cake_b200_block *b) {
   cudaSetDevice(b->device);
   void *bufs[] = {b->wqkv, b->wo, b->wgu, b->wd, b->ln1, b->ln2, b->bqkv, b->qn, b->kn, b->pan, b->pfn,
                   b->w_in, b->w_out, b->g, b->shift, b->r1, b->r2, b->m_dkv_norm, b->m_uk, b->m_uv, b->m_ukt, b->m_conv, b->m_conv_b, b->m_dt_bias,
-                  b->m_a_log, b->m_d, b->m_norm, b->m_router, b->m_corr, b->m_eg, b->m_ed, b->m_cos, b->m_sin, b->m_decay};
+                  b->m_a_log, b->m_d, b->m_norm, b->m_router, b->m_corr, b->m_eg, b->m_ed, b->m_cos, b->m_sin, b->m_decay,
+                  b->post1, b->post2, b->canon, b->b_in, b->m_ob, b->m_talk, b->m_branch, b->m_ib, b->m_fb, b->m_bias};
   for (void *p : bufs)
     if (p) cudaFree(p);  // cudaFree synchronises with outstanding work
+  if (b->side) cake_b200_block_free(b->side);
   (void)cudaGetLastError();
   delete b;
 }
@@ -768,16 +793,20 @@ extern "C" int cake_b200_cache_create(cake_b200_ctx *c, int batch, int max_seq, 
   CU(cudaSetDevice(c->device));
   auto *k = new cake_b200_cache{c, batch, max_seq, c->device};
   k->gen = g_cache_gen.fetch_add(1);
-  k->k.assign(c->cfg.n_layers, nullptr);
-  k->v.assign(c->cfg.n_layers, nullptr);
+  const int slots = c->cfg.layer_list ? 2 * c->cfg.n_layers : c->cfg.n_layers;  // a side mixer's entries follow the main ones
+  k->k.assign(slots, nullptr);
+  k->v.assign(slots, nullptr);
   k->len.assign(c->cfg.n_layers, 0);
-  k->kv_heads.assign(c->cfg.n_layers, 0);
-  k->kv_hd.assign(c->cfg.n_layers, 0);
+  k->kv_heads.assign(slots, 0);
+  k->kv_hd.assign(slots, 0);
+  k->rec_aux.assign(slots, nullptr);
+  k->canon_hist.assign(c->cfg.n_layers, nullptr);
+  k->last_tok.assign(batch, 0);
   k->shift_state[0].assign(c->cfg.n_layers, nullptr);
   k->shift_state[1].assign(c->cfg.n_layers, nullptr);
   k->shift_cur.assign(c->cfg.n_layers, 0);
-  k->rec_state.assign(c->cfg.n_layers, nullptr);
-  k->conv_hist.assign(c->cfg.n_layers, nullptr);
+  k->rec_state.assign(slots, nullptr);
+  k->conv_hist.assign(slots, nullptr);
   cudaError_t e = cudaMalloc(&k->d_pos, 4);
   if (e == cudaSuccess) e = cudaMemset(k->d_pos, 0, 4);
   if (e != cudaSuccess) {
@@ -800,6 +829,7 @@ static int cache_ensure(cake_b200_cache *k, int layer) {
 extern "C" int cake_b200_cache_clear(cake_b200_cache *k) {
   if (!k) return fail(CAKE_B200_EINVAL, "null argument");
   for (auto &l : k->len) l = 0;
+  k->embed_len = 0;  // recurrent state, histories and the previous token are ignored at position 0: nothing to wipe
   return CAKE_B200_OK;
 }
 extern "C" void cake_b200_cache_free(cake_b200_cache *k) {
@@ -829,6 +859,10 @@ extern "C" void cake_b200_cache_free(cake_b200_cache *k) {
   for (float *p : k->rec_state)
     if (p) cudaFree(p);
   for (void *p : k->conv_hist)
+    if (p) cudaFree(p);
+  for (float *p : k->rec_aux)
+    if (p) cudaFree(p);
+  for (float *p : k->canon_hist)
     if (p) cudaFree(p);
   cudaFree(k->d_pos);
   (void)cudaGetLastError();
@@ -1541,7 +1575,7 @@ static int enqueue_listed_layers(cake_b200_ctx *c, cake_b200_block *const *block
       const T *mix_in = (const T *)(b->shift ? c->sp_hs : c->sp_h);
       RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, 1, 0, (const T *)b->g, sp.scalar_norm ? 0 : 1,
                     (const T *)b->shift, (const float *)kc->shift_state[cs][l], kc->shift_state[cs ^ 1][l], (T *)c->sp_h, (T *)c->sp_hs, S, H,
-                    c->cfg.rms_eps, pos0));
+                    c->cfg.rms_eps, pos0, 0.f));
       // 2. q | k | gate logits in one product
       RowsGemm gi{mix_in, b->w_in, nullptr, c->sp_in, M, b->n_in, H, H, b->n_in_pad, 0, 0.f};
       if (listed_tc<T>(c, M, b->n_in_pad, H)) RC((listed_gemm_tc<T, TCE_PLAIN>(c, mix_in, b->w_in, nullptr, c->sp_in, M, b->n_in_pad, H, 0, 0)));
@@ -1618,10 +1652,14 @@ static void mixer_rope_tables(const cake_b200_rotary_spec &r, int rows, std::vec
     }
 }
 
+static bool mixer_kind_ext(int kind);
+static int load_mixer_ext(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer_spec *sp, const cake_b200_mixer_tensors *t, cake_b200_block **out);
 extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer_spec *sp, const cake_b200_mixer_tensors *t,
                                           cake_b200_block **out) {
   if (!c || !sp || !t || !out) return fail(CAKE_B200_EINVAL, "null argument");
   if (!c->cfg.layer_list) return fail(CAKE_B200_EINVAL, "block_load_mixer needs a ctx created with layer_list = 1");
+  if (mixer_kind_ext(sp->kind) || sp->side || sp->norm_offset != 0.f || sp->canon_taps > 1 || sp->dense_ff > 0 || t->post1 || t->post2)
+    return load_mixer_ext(c, layer_idx, sp, t, out);
   const cake_b200_moe_spec &mo = sp->moe;
   const bool has_ff = mo.experts + mo.identity > 0;
   if (sp->heads < 1 || sp->vdim < 1 || !t->norm1 || !t->o) return fail(CAKE_B200_EINVAL, "layer %d: bad heads / vdim or null norm1 / o", layer_idx);
@@ -1743,8 +1781,383 @@ extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const
   return CAKE_B200_OK;
 }
 
+// ------------------------------------------------------------------------------------------ ext blocks
+// Mixer-list blocks that use the structure switches of cake_b200_mixer_spec (gains stored as offsets, post norms, the input
+// convolution, a side mixer, a dense feed-forward) with the delta / talking-attention / matrix-memory mixers.
+static bool mixer_kind_ext(int kind) { return kind == CAKE_B200_MIX_DELTA || kind == CAKE_B200_MIX_TALKING_ATTENTION || kind == CAKE_B200_MIX_MATRIX_MEMORY; }
+static int sub_kv_heads(const cake_b200_mixer_spec &sp) { return sp.kv_heads > 0 ? sp.kv_heads : sp.heads; }
+
+// bucket of a distance: exact below rows / 2, logarithmic from there up to dmax, the last bucket beyond (double precision)
+static int distance_bucket(int n, int rows, double dmax) {
+  const int half = rows / 2;
+  if (n < half) return n;
+  if (half < 1 || !(dmax > (double)half)) return rows - 1;
+  const double v = floor(log((double)n / half) / log(dmax / half) * (double)(rows - half));
+  return (int)std::min<double>(rows - 1, half + v);
+}
+
+struct InPart { const void *w; size_t rows; const void *bias; };
+// validates one mixer of an ext block, uploads its own tensors into `b` and appends its projections to the fused input product
+static int load_sub_mixer(cake_b200_ctx *c, cake_b200_block *b, const cake_b200_mixer_spec *sp, const cake_b200_mixer_tensors *t,
+                          std::vector<InPart> &parts, size_t &row, int layer_idx) {
+  const size_t es = c->es, H = c->cfg.hidden;
+  if (sp->heads < 1 || sp->vdim < 1 || sp->dim < 1 || !t->o) return fail(CAKE_B200_EINVAL, "layer %d: bad heads / dim / vdim or null o", layer_idx);
+  const int G = sub_kv_heads(*sp);
+  if (G < 1 || sp->heads % G) return fail(CAKE_B200_EINVAL, "layer %d: %d heads over %d key heads", layer_idx, sp->heads, G);
+  const size_t inner = (size_t)sp->heads * sp->vdim;
+  auto align8 = [&]() {
+    const size_t pad = (8 - row % 8) % 8;
+    if (pad) { parts.push_back({nullptr, pad, nullptr}); row += pad; }
+  };
+  auto add = [&](const void *w, size_t rows, const void *bias) -> int {
+    const int col = (int)row;
+    parts.push_back({w, rows, bias});
+    row += rows;
+    return col;
+  };
+  b->ms = *sp;
+  b->ms.decay = nullptr;
+  b->ms.side = nullptr;
+  b->ms.kv_heads = G;
+  RC(upload(c, &b->wo, t->o, H * inner * es));
+  if (t->branch_norm) RC(upload(c, &b->m_branch, t->branch_norm, H * es));
+  if (sp->kind == CAKE_B200_MIX_DELTA) {
+    if (sp->conv < 1 || !t->q || !t->k || !t->v || !t->g || !t->q_conv || !t->k_conv || !t->v_conv || !t->beta || !t->a_proj || !t->a_log || !t->dt_bias || !t->norm)
+      return fail(CAKE_B200_EINVAL, "layer %d: the delta mixer needs conv >= 1 and q / k / v / g / their convolutions / beta / a_proj / a_log / dt_bias / norm", layer_idx);
+    const size_t qk = (size_t)G * sp->dim;
+    align8();
+    b->pc[0] = add(t->q, qk, nullptr);
+    b->pc[1] = add(t->k, qk, nullptr);
+    b->pc[2] = add(t->v, inner, nullptr);
+    align8();
+    b->pc[3] = add(t->g, inner, nullptr);
+    align8();
+    b->pc[4] = add(t->beta, sp->heads, nullptr);
+    align8();
+    b->pc[5] = add(t->a_proj, sp->heads, nullptr);
+    const size_t ch = 2 * qk + inner, tb = (size_t)sp->conv * es;   // one convolution over the channels q | k | v
+    CU(cudaMalloc(&b->m_conv, ch * tb + 16));
+    RC(pipe_copy(c, b->m_conv, qk * tb, t->q_conv, qk * tb, qk * tb, 1));
+    RC(pipe_copy(c, (char *)b->m_conv + qk * tb, qk * tb, t->k_conv, qk * tb, qk * tb, 1));
+    RC(pipe_copy(c, (char *)b->m_conv + 2 * qk * tb, inner * tb, t->v_conv, inner * tb, inner * tb, 1));
+    RC(upload(c, &b->m_dt_bias, t->dt_bias, sp->heads * es));
+    RC(upload(c, &b->m_a_log, t->a_log, sp->heads * es));
+    RC(upload(c, &b->m_norm, t->norm, (size_t)sp->vdim * es));
+  } else if (sp->kind == CAKE_B200_MIX_TALKING_ATTENTION) {
+    if (!t->q || !t->k || !t->v || (sp->bias_rows > 0 && !t->rel) || sp->bias_rows < 0)
+      return fail(CAKE_B200_EINVAL, "layer %d: talking attention needs q / k / v (and rel with bias_rows > 0)", layer_idx);
+    align8();
+    b->pc[0] = add(t->q, (size_t)sp->heads * sp->dim, t->q_b);
+    align8();
+    b->pc[1] = add(t->k, (size_t)G * sp->dim, t->k_b);
+    align8();
+    b->pc[2] = add(t->v, (size_t)G * sp->vdim, t->v_b);
+    if (t->g) {
+      align8();
+      b->pc[3] = add(t->g, inner, nullptr);
+    } else b->pc[3] = -1;
+    if (t->o_b) RC(upload(c, &b->m_ob, t->o_b, H * es));
+    if (t->talk) RC(upload(c, &b->m_talk, t->talk, (size_t)sp->heads * sp->heads * es));
+    if (sp->bias_rows > 0) {  // the bias by distance, one row per distance a cached key can have
+      const int len = c->cfg.max_seq;
+      std::vector<int> bucket(len);
+      for (int d = 0; d < len; d++) bucket[d] = distance_bucket(d, sp->bias_rows, (double)sp->bias_max);
+      void *rel = nullptr, *bk = nullptr;
+      RC(upload(c, &rel, t->rel, (size_t)sp->bias_rows * sp->heads * es));
+      int rc = upload(c, &bk, bucket.data(), (size_t)len * sizeof(int));
+      if (rc == CAKE_B200_OK) rc = pipe_mark(c);
+      if (rc == CAKE_B200_OK) rc = wait_loads(c);
+      cudaError_t e = rc == CAKE_B200_OK ? cudaMalloc(&b->m_bias, (size_t)len * sp->heads * sizeof(float)) : cudaSuccess;
+      int me = 0;
+      if (rc == CAKE_B200_OK && e == cudaSuccess) {
+        cudaStreamSynchronize(c->load_stream);  // the staging copy has left `bucket`
+        me = mx::distance_bias_table(c->stream, c->cfg.dtype, rel, (const int *)bk, b->m_bias, len, sp->heads, &c->launches);
+        cudaStreamSynchronize(c->stream);
+      }
+      if (rel) cudaFree(rel);
+      if (bk) cudaFree(bk);
+      if (rc != CAKE_B200_OK) return rc;
+      if (e != cudaSuccess || me != 0) return fail(CAKE_B200_ECUDA, "layer %d: distance bias table: %s", layer_idx, cudaGetErrorString(e != cudaSuccess ? e : (cudaError_t)me));
+      b->m_bias_len = len;
+    }
+  } else if (sp->kind == CAKE_B200_MIX_MATRIX_MEMORY) {
+    if (!t->q || !t->k || !t->v || !t->g || !t->i_proj || !t->i_b || !t->f_proj || !t->f_b || !t->norm || !(sp->gate_cap > 0.f))
+      return fail(CAKE_B200_EINVAL, "layer %d: the matrix memory needs gate_cap > 0 and q / k / v / g / i_proj / i_b / f_proj / f_b / norm", layer_idx);
+    if (G != sp->heads) return fail(CAKE_B200_EINVAL, "layer %d: the matrix memory has one key head per head", layer_idx);
+    const size_t qk = (size_t)sp->heads * sp->dim;
+    align8();
+    b->pc[0] = add(t->q, qk, nullptr);
+    align8();
+    b->pc[1] = add(t->k, qk, nullptr);
+    align8();
+    b->pc[2] = add(t->v, inner, nullptr);
+    align8();
+    b->pc[3] = add(t->g, inner, nullptr);
+    align8();
+    b->pc[4] = add(t->i_proj, sp->heads, nullptr);
+    align8();
+    b->pc[5] = add(t->f_proj, sp->heads, nullptr);
+    RC(upload(c, &b->m_ib, t->i_b, sp->heads * es));
+    RC(upload(c, &b->m_fb, t->f_b, sp->heads * es));
+    RC(upload(c, &b->m_norm, t->norm, inner * es));
+  } else return fail(CAKE_B200_EINVAL, "layer %d: mixer kind %d is not built with these block switches", layer_idx, sp->kind);
+  return CAKE_B200_OK;
+}
+
+static int load_mixer_ext(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer_spec *sp, const cake_b200_mixer_tensors *t, cake_b200_block **out) {
+  if (!t->norm1) return fail(CAKE_B200_EINVAL, "layer %d: null norm1", layer_idx);
+  if (sp->moe.experts + sp->moe.identity > 0) return fail(CAKE_B200_EINVAL, "layer %d: the routed feed-forward is not built for this block structure", layer_idx);
+  if (sp->side && (!t->side || !t->branch_norm || !t->side->branch_norm)) return fail(CAKE_B200_EINVAL, "layer %d: a side mixer needs its tensors and both branch norms", layer_idx);
+  if (sp->canon_taps < 0 || (sp->canon_taps > 1 && !t->canon)) return fail(CAKE_B200_EINVAL, "layer %d: canon_taps %d without canon", layer_idx, sp->canon_taps);
+  if (sp->dense_ff < 0 || (sp->dense_ff > 0 && (!t->ff_gate || !t->ff_up || !t->ff_down || !t->norm2 || sp->dense_act < 0 || sp->dense_act > 2)))
+    return fail(CAKE_B200_EINVAL, "layer %d: a dense feed-forward needs norm2 / ff_gate / ff_up / ff_down and dense_act in 0..2", layer_idx);
+  CU(cudaSetDevice(c->device));
+  const size_t es = c->es, H = c->cfg.hidden;
+  auto *b = new cake_b200_block{c, layer_idx, c->device};
+  b->mixer = true;
+  b->ext = true;
+  const int rc = [&]() -> int {
+    std::vector<InPart> parts;
+    size_t row = 0;
+    RC(load_sub_mixer(c, b, sp, t, parts, row, layer_idx));
+    if (sp->side) {
+      b->side = new cake_b200_block{c, layer_idx, c->device};
+      b->side->mixer = b->side->ext = true;
+      RC(load_sub_mixer(c, b->side, sp->side, t->side, parts, row, layer_idx));
+    }
+    // block-level switches live in the main block's spec
+    b->ms.norm_offset = sp->norm_offset;
+    b->ms.canon_taps = sp->canon_taps;
+    b->ms.dense_ff = sp->dense_ff;
+    b->ms.dense_act = sp->dense_act;
+    b->ms.dense_limit = sp->dense_limit;
+    b->ms.moe = cake_b200_moe_spec{};
+    b->n_in = (int)row;
+    b->n_in_pad = round_up(b->n_in, b->n_in > 1024 ? 256 : TC_BN);
+    CU(cudaMalloc(&b->w_in, (size_t)b->n_in_pad * H * es + 16));
+    CU(cudaMemsetAsync(b->w_in, 0, (size_t)b->n_in_pad * H * es, 0));
+    bool any_bias = false;
+    for (auto &pr : parts) any_bias = any_bias || pr.bias;
+    if (any_bias) {
+      CU(cudaMalloc(&b->b_in, (size_t)b->n_in_pad * es + 16));
+      CU(cudaMemsetAsync(b->b_in, 0, (size_t)b->n_in_pad * es, 0));
+    }
+    CU(cudaStreamSynchronize(0));
+    size_t r = 0;
+    for (auto &pr : parts) {
+      if (pr.w) RC(pipe_copy(c, (char *)b->w_in + r * H * es, pr.rows * H * es, pr.w, pr.rows * H * es, pr.rows * H * es, 1));
+      if (pr.bias) RC(pipe_copy(c, (char *)b->b_in + r * es, pr.rows * es, pr.bias, pr.rows * es, pr.rows * es, 1));
+      r += pr.rows;
+    }
+    RC(upload(c, &b->ln1, t->norm1, H * es));
+    if (t->post1) RC(upload(c, &b->post1, t->post1, H * es));
+    if (sp->canon_taps > 1) RC(upload(c, &b->canon, t->canon, H * sp->canon_taps * es));
+    if (sp->dense_ff > 0) {  // row-interleaved gate / up as everywhere else
+      const size_t I = sp->dense_ff;
+      RC(upload(c, &b->ln2, t->norm2, H * es));
+      if (t->post2) RC(upload(c, &b->post2, t->post2, H * es));
+      CU(cudaMalloc(&b->wgu, 2 * I * H * es + 16));
+      RC(pipe_copy(c, b->wgu, 2 * H * es, t->ff_gate, H * es, H * es, I));
+      RC(pipe_copy(c, (char *)b->wgu + H * es, 2 * H * es, t->ff_up, H * es, H * es, I));
+      RC(upload(c, &b->wd, t->ff_down, H * I * es));
+    }
+    return pipe_mark(c);
+  }();
+  if (rc != CAKE_B200_OK) {
+    cake_b200_block_free(b);
+    return rc;
+  }
+  *out = b;
+  return CAKE_B200_OK;
+}
+
+// cache entries of one mixer of an ext block at `slot` (block_idx, or n_layers + block_idx for the side mixer)
+static int cache_ensure_sub(cake_b200_cache *k, int slot, const cake_b200_block *b) {
+  cake_b200_ctx *c = k->ctx;
+  const cake_b200_mixer_spec &sp = b->ms;
+  const int G = sp.kv_heads, tag = sp.kind;
+  const int width = sp.kind == CAKE_B200_MIX_TALKING_ATTENTION ? G * (sp.dim + sp.vdim) : sp.heads * sp.dim * sp.vdim;
+  if (k->kv_heads[slot] && (k->kv_heads[slot] != tag || k->kv_hd[slot] != width))
+    return fail(CAKE_B200_ESTATE, "cache entry %d was used with another layer geometry", slot);
+  if (k->kv_heads[slot]) return CAKE_B200_OK;
+  if (sp.kind == CAKE_B200_MIX_TALKING_ATTENTION) {
+    CU(cudaMalloc(&k->k[slot], (size_t)k->batch * G * k->cap * sp.dim * c->es + 16));
+    CU(cudaMalloc(&k->v[slot], (size_t)k->batch * G * k->cap * sp.vdim * c->es + 16));
+  } else {
+    CU(cudaMalloc(&k->rec_state[slot], (size_t)k->batch * width * sizeof(float)));
+    if (sp.kind == CAKE_B200_MIX_DELTA && sp.conv > 1)
+      CU(cudaMalloc(&k->conv_hist[slot], (size_t)k->batch * (sp.conv - 1) * (2 * G * sp.dim + sp.heads * sp.vdim) * c->es + 16));
+    if (sp.kind == CAKE_B200_MIX_MATRIX_MEMORY) CU(cudaMalloc(&k->rec_aux[slot], (size_t)k->batch * sp.heads * (sp.dim + 1) * sizeof(float)));
+  }
+  k->kv_heads[slot] = tag;
+  k->kv_hd[slot] = width;
+  return CAKE_B200_OK;
+}
+static int cache_ensure_ext(cake_b200_cache *k, int layer, const cake_b200_block *b) {
+  const int nl = (int)k->len.size();
+  if ((int)k->k.size() < 2 * nl) return fail(CAKE_B200_EINVAL, "the cache was not created for a layer-list model");
+  RC(cache_ensure_sub(k, layer, b));
+  if (b->side) RC(cache_ensure_sub(k, nl + layer, b->side));
+  if (b->ms.canon_taps > 1 && !k->canon_hist[layer])
+    CU(cudaMalloc(&k->canon_hist[layer], (size_t)k->batch * (b->ms.canon_taps - 1) * k->ctx->cfg.hidden * sizeof(float)));
+  return CAKE_B200_OK;
+}
+
+// scratch of one mixer of an ext block
+struct SubScratch {
+  void *att, *conv;
+  float *o32, *qn, *kn, *f1, *f2, *f3, *part, *y;
+  int nsplit;
+};
+constexpr int TALK_SPLIT_MAX = 64;
+template <typename Take> static SubScratch sub_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, int n_keys, Take &&take) {
+  SubScratch s{};
+  const cake_b200_mixer_spec &sp = b->ms;
+  const size_t es = c->es, inner = (size_t)sp.heads * sp.vdim, G = sp.kv_heads;
+  s.att = take(M * inner * es);
+  s.y = (float *)take(M * c->cfg.hidden * sizeof(float));
+  if (sp.kind == CAKE_B200_MIX_TALKING_ATTENTION) {
+    // steps of a few rows over many keys: split the keys so that the step fills the chip
+    if (M <= 32 && n_keys >= 256) {
+      s.nsplit = (int)std::min<size_t>(TALK_SPLIT_MAX, std::min<size_t>((n_keys + 127) / 128, (2 * (size_t)c->sm_count + M - 1) / M));
+      if (s.nsplit > 1) s.part = (float *)take(M * s.nsplit * (2 * (size_t)sp.heads + inner) * sizeof(float));
+      else s.nsplit = 0;
+    }
+    return s;
+  }
+  s.o32 = (float *)take(M * inner * sizeof(float));
+  s.f1 = (float *)take(M * sp.heads * sizeof(float));
+  s.f2 = (float *)take(M * sp.heads * sizeof(float));
+  if (sp.kind == CAKE_B200_MIX_DELTA) {
+    s.conv = take(M * (2 * G * sp.dim + inner) * es);
+    s.qn = (float *)take(M * G * sp.dim * sizeof(float));
+    s.kn = (float *)take(M * G * sp.dim * sizeof(float));
+  } else s.f3 = (float *)take(M * sp.heads * sizeof(float));
+  return s;
+}
+struct ExtScratch {
+  void *h, *proj, *act;
+  float *h32;
+  SubScratch a, b;
+  size_t total;
+};
+static ExtScratch ext_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, char *base, int n_keys) {
+  ExtScratch s{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) -> void * {
+    void *p = base ? base + off : nullptr;
+    off += (bytes + 255) / 256 * 256;
+    return p;
+  };
+  const size_t es = c->es, H = c->cfg.hidden;
+  s.h = take(M * H * es);
+  if (b->ms.canon_taps > 1) s.h32 = (float *)take(M * H * sizeof(float));
+  s.proj = take(M * b->n_in_pad * es);
+  s.a = sub_scratch(c, b, M, n_keys, take);
+  if (b->side) s.b = sub_scratch(c, b->side, M, n_keys, take);
+  if (b->ms.dense_ff > 0) s.act = take(M * (size_t)b->ms.dense_ff * es);
+  s.total = off;
+  return s;
+}
+
+// C (fp32 [M, N]) = A[M, K] W[N, K]^T
+template <typename T> static int gemm_f32_out(cake_b200_ctx *c, const void *A, const void *W, float *C, int M, int N, int K) {
+  if (listed_tc<T>(c, M, N, K)) return listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, A, W, nullptr, C, M, N, K, 0, 0);
+  RowsGemm g{A, W, nullptr, C, M, N, K, K, N, 0, 0.f};
+  return gemm_rows_T<T, RE_SOFTCAP_F32>(c, g);
+}
+template <typename T> static int gemm_bias_tc(cake_b200_ctx *c, const void *A, const void *W, const void *bias, void *C, int M, int N, int K) {
+  return gemm_tc_T<T, TCE_PLAIN>(c, A, W, bias, nullptr, C, M, N, K, 0, 0);
+}
+template <> int gemm_bias_tc<float>(cake_b200_ctx *, const void *, const void *, const void *, void *, int, int, int) { return CAKE_B200_EINVAL; }
+
+// one mixer of an ext block: proj [M, ldp] holds its projections at b->pc[]; y [M, hidden] fp32 receives o(att) without o's bias
+template <typename T>
+static int run_sub_mixer(cake_b200_ctx *c, const cake_b200_block *b, cake_b200_cache *kc, int slot, const SubScratch &w, const T *proj, int ldp,
+                         int B, int S, int pos0, uint64_t *lc) {
+  const cake_b200_mixer_spec &sp = b->ms;
+  const int M = B * S, H = c->cfg.hidden, dt = c->cfg.dtype, G = sp.kv_heads, inner = sp.heads * sp.vdim;
+  cudaStream_t st = c->stream;
+  if (sp.kind == CAKE_B200_MIX_DELTA) {
+    const int qk = G * sp.dim, ch = 2 * qk + inner;
+    const T *cv = (const T *)w.conv;
+    mx::ShortConv sc{proj, ldp, b->pc[0], b->m_conv, nullptr, kc->conv_hist[slot], w.conv, B, S, ch, sp.conv, pos0};
+    MX(mx::short_conv(st, dt, sc, lc));
+    mx::DeltaPrep dp{cv, cv + qk, ch, proj + b->pc[4], proj + b->pc[5], ldp, b->m_a_log, b->m_dt_bias, w.qn, w.kn, w.f1, w.f2, M, sp.heads, G, sp.dim,
+                     1.0f / sqrtf((float)sp.dim)};
+    MX(mx::delta_prep(st, dt, dp, lc));
+    mx::DeltaRule dr{w.qn, w.kn, cv + 2 * qk, ch, w.f1, w.f2, kc->rec_state[slot], w.o32, B, S, sp.heads, G, sp.dim, sp.vdim, pos0};
+    MX(mx::delta_rule(st, dt, dr, lc));
+    mx::GateNorm gn{w.o32, proj + b->pc[3], ldp, b->m_norm, w.att, M, inner, sp.heads, 0, c->cfg.rms_eps, 0, sp.vdim, nullptr};
+    MX(mx::gate_norm(st, dt, gn, lc));
+  } else if (sp.kind == CAKE_B200_MIX_TALKING_ATTENTION) {
+    RC(launch_pdl(c, rows_to_cache_kernel<T>, dim3(M), dim3(128), 0, proj, (T *)kc->k[slot], S, ldp, b->pc[1], G, sp.dim, kc->cap, pos0));
+    RC(launch_pdl(c, rows_to_cache_kernel<T>, dim3(M), dim3(128), 0, proj, (T *)kc->v[slot], S, ldp, b->pc[2], G, sp.vdim, kc->cap, pos0));
+    mx::TalkAttn ta{proj + b->pc[0], ldp, kc->k[slot], kc->v[slot], b->pc[3] >= 0 ? proj + b->pc[3] : nullptr, ldp, b->m_bias, b->m_bias_len, b->m_talk,
+                    w.att, B, S, sp.heads, G, sp.dim, sp.vdim, kc->cap, pos0, sp.scale, w.part, w.nsplit};
+    MX(mx::talk_attention(st, dt, ta, lc));
+  } else {
+    const float qs = 1.0f / sqrtf((float)sp.dim);
+    mx::GatePrep gp{proj + b->pc[0], proj + b->pc[1], ldp, proj + b->pc[4], proj + b->pc[5], ldp, b->m_ib, b->m_fb, kc->rec_aux[slot], w.f1, w.f2, w.f3,
+                    B, S, sp.heads, sp.dim, pos0, sp.gate_cap, qs};
+    MX(mx::gate_prep(st, dt, gp, lc));
+    mx::Recurrence r{proj + b->pc[0], proj + b->pc[1], proj + b->pc[2], ldp, ldp, ldp, 1, nullptr, 0, nullptr, nullptr, nullptr, nullptr, 1.0f,
+                     nullptr, nullptr, 0, kc->rec_state[slot], w.o32, B, S, sp.heads, sp.dim, sp.vdim, pos0, w.f1, w.f2};
+    MX(mx::recurrence(st, dt, r, lc));
+    mx::GateNorm gn{w.o32, proj + b->pc[3], ldp, b->m_norm, w.att, M, inner, sp.heads, 0, c->cfg.rms_eps, 1, 0, w.f3};
+    MX(mx::gate_norm(st, dt, gn, lc));
+  }
+  return gemm_f32_out<T>(c, w.att, b->wo, w.y, M, H, inner);
+}
+
+// one ext block: x_out = x + post1(mixers(canon(norm1(x)))), then x_out += post2(ff(norm2(x_out)))
+template <typename T>
+static int enqueue_ext_layer(cake_b200_ctx *c, const cake_b200_block *b, int l, cake_b200_cache *kc, const float *cur, float *x_out, int B, int S, int pos0,
+                             uint64_t *lc) {
+  const cake_b200_mixer_spec &sp = b->ms;
+  const int M = B * S, H = c->cfg.hidden, dt = c->cfg.dtype, nl = (int)kc->len.size();
+  const float eps = c->cfg.rms_eps;
+  cudaStream_t st = c->stream;
+  const ExtScratch w = ext_scratch(c, b, (size_t)M, (char *)c->mx_ws, pos0 + S);
+  // 1. h = norm1(x), the input convolution, every projection of the mixer(s) in one product
+  mx::RmsRows n1{cur, b->ln1, sp.norm_offset, sp.canon_taps > 1 ? w.h32 : nullptr, sp.canon_taps > 1 ? nullptr : w.h, M, H, eps};
+  MX(mx::rms_rows(st, dt, n1, lc));
+  if (sp.canon_taps > 1) {
+    mx::CanonConv cc{w.h32, b->canon, kc->canon_hist[l], w.h, B, S, H, sp.canon_taps, pos0};
+    MX(mx::canon_conv(st, dt, cc, lc));
+  }
+  if (listed_tc<T>(c, M, b->n_in_pad, H)) RC(gemm_bias_tc<T>(c, w.h, b->w_in, b->b_in, w.proj, M, b->n_in_pad, H));
+  else {
+    RowsGemm gi{w.h, b->w_in, nullptr, w.proj, M, b->n_in, H, H, b->n_in_pad, 0, 0.f, nullptr, b->b_in};
+    RC((gemm_rows_T<T, RE_STORE>(c, gi)));
+  }
+  // 2. the mixer(s), each up to its output projection in fp32
+  RC(run_sub_mixer<T>(c, b, kc, l, w.a, (const T *)w.proj, b->n_in_pad, B, S, pos0, lc));
+  if (b->side) RC(run_sub_mixer<T>(c, b->side, kc, nl + l, w.b, (const T *)w.proj, b->n_in_pad, B, S, pos0, lc));
+  // 3. x <- x + post1(branches)
+  mx::BranchMerge bm{w.a.y, b->side ? w.b.y : nullptr, b->m_ob, b->side ? b->side->m_ob : nullptr, b->m_branch, b->side ? b->side->m_branch : nullptr,
+                     b->post1, sp.norm_offset, cur, x_out, M, H, eps};
+  MX(mx::branch_merge(st, dt, bm, lc));
+  // 4. x <- x + post2(ff(norm2(x)))
+  if (sp.dense_ff > 0) {
+    const int I = sp.dense_ff;
+    mx::RmsRows n2{x_out, b->ln2, sp.norm_offset, nullptr, w.h, M, H, eps};
+    MX(mx::rms_rows(st, dt, n2, lc));
+    if (listed_tc<T>(c, M, 2 * I, H)) RC((listed_gemm_tc<T, TCE_SWIGLU>(c, w.h, b->wgu, nullptr, w.act, M, 2 * I, H, sp.dense_act, I, sp.dense_limit)));
+    else {
+      RowsGemm gu{w.h, b->wgu, nullptr, w.act, M, 2 * I, H, H, I, sp.dense_act, sp.dense_limit};
+      RC((gemm_rows_T<T, RE_GATE_UP>(c, gu)));
+    }
+    RC(gemm_f32_out<T>(c, w.act, b->wd, w.a.y, M, H, I));
+    mx::BranchMerge fm{w.a.y, nullptr, nullptr, nullptr, nullptr, nullptr, b->post2, sp.norm_offset, x_out, x_out, M, H, eps};
+    MX(mx::branch_merge(st, dt, fm, lc));
+  }
+  return CAKE_B200_OK;
+}
+
 static int cache_ensure_mixer(cake_b200_cache *k, int layer, const cake_b200_block *b) {
-  if (layer < 0 || layer >= (int)k->k.size()) return fail(CAKE_B200_EINVAL, "block_idx %d out of range", layer);
+  if (layer < 0 || layer >= (int)k->len.size()) return fail(CAKE_B200_EINVAL, "block_idx %d out of range", layer);
+  if (b->ext) return cache_ensure_ext(k, layer, b);
   cake_b200_ctx *c = k->ctx;
   const cake_b200_mixer_spec &sp = b->ms;
   // (kind, row width) a slot was first used with: a slot never changes its layer
@@ -1842,7 +2255,8 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
   const int H = c->cfg.hidden, M = B * S, dt = c->cfg.dtype;
   size_t need = 0;
   for (int i = 0; i < n; i++) {
-    need = std::max(need, mixer_scratch(c, blocks[i], (size_t)M, nullptr, S, pos0 + S).total);
+    need = std::max(need, blocks[i]->ext ? ext_scratch(c, blocks[i], (size_t)M, nullptr, pos0 + S).total
+                                         : mixer_scratch(c, blocks[i], (size_t)M, nullptr, S, pos0 + S).total);
     if (blocks[i]->m_cos && pos0 + S > blocks[i]->m_rope_rows)
       return fail(CAKE_B200_ESTATE, "position %d exceeds the rotation table (%d rows = the ctx's max_seq)", pos0 + S, blocks[i]->m_rope_rows);
   }
@@ -1863,10 +2277,15 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
       const cake_b200_block *b = blocks[i];
       const cake_b200_mixer_spec &sp = b->ms;
       const int l = block_idx[i], inner = sp.heads * sp.vdim;
+      if (b->ext) {
+        RC(enqueue_ext_layer<T>(c, b, l, kc, cur, x_out, B, S, pos0, lc));
+        cur = x_out;
+        continue;
+      }
       const MixerScratch w = mixer_scratch(c, b, (size_t)M, (char *)c->mx_ws, S, pos0 + S);
       // 1. h = norm1(x); every input projection of the mixer in one product
       RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, 1, 0, (const T *)b->ln1, 1, (const T *)nullptr,
-                    (const float *)nullptr, (float *)nullptr, (T *)w.h, (T *)nullptr, S, H, c->cfg.rms_eps, pos0));
+                    (const float *)nullptr, (float *)nullptr, (T *)w.h, (T *)nullptr, S, H, c->cfg.rms_eps, pos0, 0.f));
       RowsGemm gi{w.h, b->w_in, nullptr, w.proj, M, b->n_in, H, H, b->n_in_pad, 0, 0.f};
       if (listed_tc<T>(c, M, b->n_in_pad, H)) RC((listed_gemm_tc<T, TCE_PLAIN>(c, w.h, b->w_in, nullptr, w.proj, M, b->n_in_pad, H, 0, 0)));
       else RC((gemm_rows_T<T, RE_STORE>(c, gi)));
@@ -1952,7 +2371,7 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
       const cake_b200_moe_spec &mo = sp.moe;
       if (mo.experts + mo.identity > 0) {
         RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, 1, 0, (const T *)b->ln2, 1, (const T *)nullptr,
-                      (const float *)nullptr, (float *)nullptr, (T *)w.h, (T *)nullptr, S, H, c->cfg.rms_eps, pos0));
+                      (const float *)nullptr, (float *)nullptr, (T *)w.h, (T *)nullptr, S, H, c->cfg.rms_eps, pos0, 0.f));
         const int NP = round_up(mo.experts + mo.identity + 1, TC_BN);
         RowsGemm gr{w.h, b->m_router, nullptr, w.logits, M, NP, H, H, NP, 0, 0.f};
         if (listed_tc<T>(c, M, NP, H)) RC((listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, w.h, b->m_router, nullptr, w.logits, M, NP, H, 0, 0)));
@@ -2144,6 +2563,56 @@ extern "C" int cake_b200_embed(cake_b200_ctx *c, const uint32_t *ids_host, int b
 }
 
 
+extern "C" int cake_b200_head_load_tables(cake_b200_ctx *c, const cake_b200_embed_tables *t) {
+  if (!c || !t) return fail(CAKE_B200_EINVAL, "null argument");
+  if (!c->cfg.layer_list) return fail(CAKE_B200_EINVAL, "head_load_tables is for models with an fp32 residual stream");
+  if ((t->bigram && (t->bigram_rows < 2 || t->mul_prev < 0 || t->mul_cur < 0)) || (t->pos && t->pos_rows < 1)) return fail(CAKE_B200_EINVAL, "bad embedding table sizes");
+  CU(cudaSetDevice(c->device));
+  const size_t H = c->cfg.hidden;
+  if (t->bigram) {
+    RC(upload(c, &c->bigram, t->bigram, (size_t)t->bigram_rows * H * c->es));
+    c->bigram_rows = t->bigram_rows;
+    c->mul_prev = t->mul_prev;
+    c->mul_cur = t->mul_cur;
+  }
+  if (t->pos) {
+    RC(upload(c, &c->pos_tab, t->pos, (size_t)t->pos_rows * H * c->es));
+    c->pos_rows = t->pos_rows;
+  }
+  c->final_norm_offset = t->final_norm_offset;
+  return pipe_mark(c);
+}
+
+extern "C" int cake_b200_embed_at(cake_b200_ctx *c, cake_b200_cache *kc, const uint32_t *ids_host, int batch, int seq, int index_pos, void *x_dev) {
+  if (!c || !kc || !ids_host || !x_dev || !c->embed) return fail(CAKE_B200_EINVAL, "null argument or head not loaded");
+  if (!c->cfg.layer_list) return fail(CAKE_B200_EINVAL, "embed_at is for models with an fp32 residual stream");
+  if (batch < 1 || seq < 1 || batch != kc->batch) return fail(CAKE_B200_EINVAL, "embed_at: batch %d (cache batch %d) / seq %d", batch, kc ? kc->batch : 0, seq);
+  if (index_pos != kc->embed_len) return fail(CAKE_B200_ESTATE, "embed_at: index_pos %d != the position %d the embedding has reached in this cache", index_pos, kc->embed_len);
+  if (c->pos_tab && index_pos + seq > c->pos_rows) return fail(CAKE_B200_ESTATE, "position %d exceeds the %d learned positions", index_pos + seq, c->pos_rows);
+  CU(cudaSetDevice(c->device));
+  RC(wait_loads(c));
+  const size_t n = (size_t)batch * seq;
+  for (size_t i = 0; i < n; i++)
+    if (ids_host[i] >= (uint32_t)c->cfg.vocab) return fail(CAKE_B200_EINVAL, "token id %u at %zu out of range (vocab %d)", ids_host[i], i, c->cfg.vocab);
+  if (n + batch > c->d_ids_cap) {
+    CU(cudaStreamSynchronize(c->stream));
+    if (c->d_ids) cudaFree(c->d_ids);
+    c->d_ids = nullptr;
+    c->d_ids_cap = 0;
+    CU(cudaMalloc(&c->d_ids, (n + batch) * 4));
+    c->d_ids_cap = n + batch;
+  }
+  CU(cudaMemcpyAsync(c->d_ids, ids_host, n * 4, cudaMemcpyHostToDevice, c->stream));
+  CU(cudaMemcpyAsync(c->d_ids + n, kc->last_tok.data(), (size_t)batch * 4, cudaMemcpyHostToDevice, c->stream));
+  CU(cudaStreamSynchronize(c->stream));  // both sources are pageable host memory that changes below / belongs to the caller
+  mx::EmbedTables et{c->embed, c->d_ids, c->bigram, c->pos_tab, (float *)x_dev, batch, seq, c->cfg.hidden, c->cfg.vocab, c->bigram_rows - 1,
+                     c->mul_prev, c->mul_cur, index_pos, c->cfg.embed_scale};
+  MX(mx::embed_tables(c->stream, c->cfg.dtype, et, &c->launches));
+  for (int b = 0; b < batch; b++) kc->last_tok[b] = ids_host[(size_t)b * seq + seq - 1];
+  kc->embed_len = index_pos + seq;
+  return CAKE_B200_OK;
+}
+
 // fp32 logits of n rows of the fp32 stream: final norm (scalar or vector gain) -> lm_head -> soft cap
 // rows_host == NULL: row i = i * row_mul + row_add (no table, nothing to wait for)
 static int listed_logits(cake_b200_ctx *c, const void *x_dev, const int *rows_host, int row_mul, int row_add, int n, float *out_dev) {
@@ -2168,7 +2637,7 @@ static int listed_logits(cake_b200_ctx *c, const void *x_dev, const int *rows_ho
     RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(n), dim3(256), 0, (const float *)x_dev, (const int *)(rows_host ? c->sp_rows_idx : nullptr),
                   row_mul, row_add, (const T *)c->ln_f,
                   c->cfg.scalar_final_norm ? 0 : 1, (const T *)nullptr, (const float *)nullptr, (float *)nullptr, (T *)c->sp_hn, (T *)nullptr, 1,
-                  (int)H, c->cfg.rms_eps, 0));
+                  (int)H, c->cfg.rms_eps, 0, c->final_norm_offset));
     RowsGemm g{c->sp_hn, c->lm_head, nullptr, out_dev ? out_dev : c->sp_logits, n, (int)V, (int)H, (int)H, (int)V, 0, c->cfg.logit_softcap};
     if (listed_tc<T>(c, n, (int)V, (int)H))
       return listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, c->sp_hn, c->lm_head, nullptr, g.C, n, (int)V, (int)H, 0, 0, c->cfg.logit_softcap);

@@ -62,6 +62,19 @@ template <typename T> __device__ __forceinline__ float gate_act(float g, int act
   return rnd<T>(g / (1.0f + expf(-g)));
 }
 
+// act(gate) * up of a gated feed-forward from the two fp32 accumulators.  act 0 / 1: as gate_act.  act 2, the clamped form:
+// g' = min(g, lim), u' = clamp(u, -lim, lim), g' * sigmoid(1.702 g') * (u' + 1).
+template <typename T> __device__ __forceinline__ float gated_pair(float g, float u, int act, float lim) {
+  g = rnd<T>(g);
+  u = rnd<T>(u);
+  if (act == 2) {
+    g = fminf(g, lim);
+    u = fminf(fmaxf(u, -lim), lim);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+  }
+  return gate_act<T>(g, act) * u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

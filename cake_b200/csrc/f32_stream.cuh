@@ -67,7 +67,8 @@ __global__ void __launch_bounds__(256) norm_shift_rows_kernel(const float *__res
                                                               const T *__restrict__ g, int g_stride,
                                                               const T *__restrict__ shift, const float *__restrict__ state_in,
                                                               float *__restrict__ state_out, T *__restrict__ h_out,
-                                                              T *__restrict__ hs_out, int S, int n, float eps, int pos0) {
+                                                              T *__restrict__ hs_out, int S, int n, float eps, int pos0,
+                                                              float g_add /* gain = g + g_add: gains stored as offsets */) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[2][8];
@@ -117,7 +118,7 @@ __global__ void __launch_bounds__(256) norm_shift_rows_kernel(const float *__res
       const float4 v = x4[i];
       float gi[4], h[4];
 #pragma unroll
-      for (int e = 0; e < 4; e++) gi[e] = DT<T>::to_f(g[(size_t)(4 * i + e) * g_stride]);
+      for (int e = 0; e < 4; e++) gi[e] = DT<T>::to_f(g[(size_t)(4 * i + e) * g_stride]) + g_add;
       h[0] = v.x * inv * gi[0]; h[1] = v.y * inv * gi[1]; h[2] = v.z * inv * gi[2]; h[3] = v.w * inv * gi[3];
       if (h_out) store4<T>(h_out + (size_t)r * n + 4 * i, h[0], h[1], h[2], h[3]);
       if (shifted) {
@@ -139,7 +140,7 @@ __global__ void __launch_bounds__(256) norm_shift_rows_kernel(const float *__res
     return;
   }
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float gi = DT<T>::to_f(g[(size_t)i * g_stride]);
+    const float gi = DT<T>::to_f(g[(size_t)i * g_stride]) + g_add;
     const float h = xr[i] * inv * gi;
     if (h_out) h_out[(size_t)r * n + i] = DT<T>::from_f(h);
     if (shifted) {
@@ -158,9 +159,10 @@ struct RowsGemm {
   const float *R;   // RE_RESIDUAL_F32: [M, N] fp32
   void *C;          // RE_STORE: [M, ldc] D;  RE_GATE_UP: [M, ldc] D, N/2 columns written;  else [M, N] fp32
   int M, N, K, lda, ldc;
-  int act;          // RE_GATE_UP: 0 silu, 1 tanh-gelu
+  int act;          // RE_GATE_UP: 0 silu, 1 tanh-gelu, 2 clamped (gated_pair; the limit travels in cap)
   float cap;        // RE_SOFTCAP_F32: 0 = none
   const float *rs = nullptr;  // RE_RESIDUAL_F32: optional [M] fp32, C = R + rs[m] * (A W^T) (a per-row gate on the product)
+  const void *bias = nullptr; // RE_STORE: optional [N] D added to the fp32 sum before it is rounded
 };
 constexpr int RG_BM = 64, RG_BN = 64, RG_BK = 16;
 template <typename T, int EPI>
@@ -202,14 +204,14 @@ __global__ void __launch_bounds__(256) gemm_rows_kernel(const RowsGemm p) {
 #pragma unroll
       for (int j = 0; j < 4; j += 2) {
         const int n = n0 + tx * 4 + j;
-        if (n + 1 < p.N) C[(size_t)m * p.ldc + n / 2] = DT<T>::from_f(gate_act<T>(rnd<T>(acc[i][j]), p.act) * rnd<T>(acc[i][j + 1]));
+        if (n + 1 < p.N) C[(size_t)m * p.ldc + n / 2] = DT<T>::from_f(gated_pair<T>(acc[i][j], acc[i][j + 1], p.act, p.cap));
       }
     } else {
 #pragma unroll
       for (int j = 0; j < 4; j++) {
         const int n = n0 + tx * 4 + j;
         if (n >= p.N) continue;
-        if (EPI == RE_STORE) reinterpret_cast<T *>(p.C)[(size_t)m * p.ldc + n] = DT<T>::from_f(acc[i][j]);
+        if (EPI == RE_STORE) reinterpret_cast<T *>(p.C)[(size_t)m * p.ldc + n] = DT<T>::from_f(p.bias ? acc[i][j] + DT<T>::to_f(reinterpret_cast<const T *>(p.bias)[n]) : acc[i][j]);
         else if (EPI == RE_RESIDUAL_F32) reinterpret_cast<float *>(p.C)[(size_t)m * p.N + n] = p.R[(size_t)m * p.N + n] + (p.rs ? p.rs[m] * acc[i][j] : acc[i][j]);
         else reinterpret_cast<float *>(p.C)[(size_t)m * p.N + n] = p.cap > 0.f ? p.cap * tanhf(acc[i][j] / p.cap) : acc[i][j];
       }

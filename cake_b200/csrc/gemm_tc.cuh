@@ -45,10 +45,10 @@ struct TcParams {
   const void *residual;  // [M,N] D (TCE_RESIDUAL)
   void *C;               // [M,N] D  ([M,N/2] for TCE_SWIGLU)
   int M, N, K;
-  int act;  // TCE_SWIGLU: 0 silu, 1 gelu_tanh
+  int act;  // TCE_SWIGLU: 0 silu, 1 gelu_tanh, 2 the clamped form of gated_pair (its limit travels in cap)
   int ldc;  // TCE_SWIGLU / TCE_PLAIN: row stride of C in elements when it is a column range of a wider buffer (0 = N/2 resp. N;
             // a multiple of 8, like the column offset folded into C)
-  float cap; // TCE_SOFTCAP_F32
+  float cap; // TCE_SOFTCAP_F32; TCE_SWIGLU with act 2: the limit
   // grouped product (a routed feed-forward): the rows of A are sorted by group in blocks of TC_BM rows, tile_group[m0 / TC_BM]
   // names the group of a row block (< 0: the block is empty and skipped), and group g multiplies by rows g * N .. g * N + N - 1
   // of W (map_b covers all groups).  nullptr: one group.
@@ -281,9 +281,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               float v[2];
 #pragma unroll
               for (int h = 0; h < 2; h++) {
-                const float g = rnd<T>(__uint_as_float(r[4 * j + 2 * h])), u = rnd<T>(__uint_as_float(r[4 * j + 2 * h + 1]));
-                const float sl = gate_act<T>(g, p.act);
-                v[h] = sl * u;
+                v[h] = gated_pair<T>(__uint_as_float(r[4 * j + 2 * h]), __uint_as_float(r[4 * j + 2 * h + 1]), p.act, p.cap);
               }
               o[j] = pack2<T>(v[0], v[1]);
             }

@@ -459,8 +459,12 @@ __global__ void recurrence_kernel(const Recurrence p) {
       a = expf(nexpA * d);
       bsc = d;
     } else {
-      a = p.decay[h];
+      a = p.decay ? p.decay[h] : 1.f;
       bsc = p.kscale;
+    }
+    if (p.a_tok) {
+      a = p.a_tok[m * p.heads + h];
+      bsc = p.b_tok[m * p.heads + h];
     }
     const float *cs = p.cos_t ? p.cos_t + (size_t)(p.pos0 + t) * half : nullptr, *sn = p.sin_t ? p.sin_t + (size_t)(p.pos0 + t) * half : nullptr;
     for (int i = threadIdx.x; i < dk; i += blockDim.x) {
@@ -561,6 +565,10 @@ __global__ void __launch_bounds__(256, R > 16 ? 1 : (ROPE ? 2 : 3)) recurrence_c
         const float d = softplus_f(DT<T>::to_f(rdt) + bias);
         a = expf(nexpA * d);
         bsc = d;
+      }
+      if (p.a_tok) {
+        a = p.a_tok[(m0 + threadIdx.x) * p.heads + h];
+        bsc = p.b_tok[(m0 + threadIdx.x) * p.heads + h];
       }
       as[threadIdx.x] = a;
       bs[threadIdx.x] = bsc;
@@ -688,7 +696,7 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const ShortConv p) {
   const T *hist = reinterpret_cast<const T *>(p.hist) + (size_t)b * back * p.channels;
   T *out = reinterpret_cast<T *>(p.out) + (size_t)m * p.channels;
   for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < p.channels; ch += gridDim.y * blockDim.x) {
-    float acc = DT<T>::to_f(bias[ch]);
+    float acc = bias ? DT<T>::to_f(bias[ch]) : 0.f;
     for (int jt = 0; jt < p.taps; jt++) {
       const int tt = t - back + jt;
       float x = 0.f;
@@ -725,7 +733,11 @@ __global__ void __launch_bounds__(128) short_conv_vec_kernel(const ShortConv p) 
     for (int e = 0; e < 8; e++)
 #pragma unroll
       for (int jt = 0; jt < TAPS; jt++) w[e][jt] = tmp[e * TAPS + jt];
-    unpack8<T>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.bias) + ch), bias);
+    if (p.bias) unpack8<T>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.bias) + ch), bias);
+    else {
+#pragma unroll
+      for (int e = 0; e < 8; e++) bias[e] = 0.f;
+    }
   }
 #pragma unroll
   for (int jt = 0; jt < TAPS - 1; jt++) {  // the rows before the chunk: this step's, the history's, or zeros before position 0
@@ -804,8 +816,11 @@ __global__ void __launch_bounds__(128) gate_norm_kernel(const GateNorm p) {
   const int m = (int)(warp / p.parts), g = (int)(warp % p.parts), len = p.n / p.parts, c0 = g * len;
   const float *o = p.o + (size_t)m * p.n + c0;
   const T *gate = reinterpret_cast<const T *>(p.gate) + (size_t)m * p.ldg + c0;
-  const T *w = p.w ? reinterpret_cast<const T *>(p.w) + c0 : nullptr;
+  const T *w = p.w ? reinterpret_cast<const T *>(p.w) + (p.w_period ? 0 : c0) : nullptr;  // w_period == len: every part reads the same gains
   T *out = reinterpret_cast<T *>(p.out) + (size_t)m * p.n + c0;
+  const float rdiv = p.row_div ? p.row_div[(size_t)m * p.parts + g] : 1.f;
+  const bool sg = p.gate_sigmoid != 0;
+  auto gact = [sg](float z) { return sg ? 1.0f / (1.0f + expf(-z)) : silu_f(z); };
   float ss = 0.f;
   // parts whose rows start on 16 bytes: four entries per lane and load
   const bool vec = sizeof(T) == 2 && (len & 3) == 0 && (p.n & 3) == 0 && (p.ldg & 3) == 0 &&
@@ -817,10 +832,11 @@ __global__ void __launch_bounds__(128) gate_norm_kernel(const GateNorm p) {
     for (int i = lane; i < len / 4; i += 32) {
       const float4 ov = o4[i];
       float v[4] = {ov.x, ov.y, ov.z, ov.w};
+      if (p.row_div) { v[0] /= rdiv; v[1] /= rdiv; v[2] /= rdiv; v[3] /= rdiv; }
       if (p.gate_first) {
         const uint2 g = g2[i];
         const float2 ga = DT<B>::unpack2(g.x), gb = DT<B>::unpack2(g.y);
-        v[0] *= silu_f(ga.x); v[1] *= silu_f(ga.y); v[2] *= silu_f(gb.x); v[3] *= silu_f(gb.y);
+        v[0] *= gact(ga.x); v[1] *= gact(ga.y); v[2] *= gact(gb.x); v[3] *= gact(gb.y);
       }
       ss = fmaf(v[0], v[0], ss); ss = fmaf(v[1], v[1], ss); ss = fmaf(v[2], v[2], ss); ss = fmaf(v[3], v[3], ss);
     }
@@ -830,8 +846,9 @@ __global__ void __launch_bounds__(128) gate_norm_kernel(const GateNorm p) {
       const float4 ov = o4[i];
       const uint2 g = g2[i];
       const float2 ga = DT<B>::unpack2(g.x), gb = DT<B>::unpack2(g.y);
-      const float gs[4] = {silu_f(ga.x), silu_f(ga.y), silu_f(gb.x), silu_f(gb.y)};
+      const float gs[4] = {gact(ga.x), gact(ga.y), gact(gb.x), gact(gb.y)};
       float v[4] = {ov.x, ov.y, ov.z, ov.w};
+      if (p.row_div) { v[0] /= rdiv; v[1] /= rdiv; v[2] /= rdiv; v[3] /= rdiv; }
       float wv[4] = {1.f, 1.f, 1.f, 1.f};
       if (w) {
         const uint2 ww = w2[i];
@@ -850,21 +867,23 @@ __global__ void __launch_bounds__(128) gate_norm_kernel(const GateNorm p) {
     return;
   }
   for (int i = lane; i < len; i += 32) {
-    const float v = p.gate_first ? o[i] * silu_f(DT<T>::to_f(gate[i])) : o[i];
+    const float ov = p.row_div ? o[i] / rdiv : o[i];
+    const float v = p.gate_first ? ov * gact(DT<T>::to_f(gate[i])) : ov;
     ss = fmaf(v, v, ss);
   }
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)len + p.eps);
   for (int i = lane; i < len; i += 32) {
-    const float gs = silu_f(DT<T>::to_f(gate[i]));
-    float v = (p.gate_first ? o[i] * gs : o[i]) * inv;
+    const float gs = gact(DT<T>::to_f(gate[i]));
+    const float ov = p.row_div ? o[i] / rdiv : o[i];
+    float v = (p.gate_first ? ov * gs : ov) * inv;
     if (w) v *= DT<T>::to_f(w[i]);
     if (!p.gate_first) v *= gs;
     out[i] = DT<T>::from_f(v);
   }
 }
 int gate_norm(cudaStream_t st, int dtype, const GateNorm &p, uint64_t *launches) {
-  if (p.parts < 1 || p.n % p.parts) return (int)cudaErrorInvalidValue;
+  if (p.parts < 1 || p.n % p.parts || (p.w_period && p.w_period != p.n / p.parts)) return (int)cudaErrorInvalidValue;
   const long warps = (long)p.M * p.parts;
   MX_DISPATCH(dtype, (gate_norm_kernel<T><<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(p)));
   MX_DONE(1);
@@ -1156,6 +1175,608 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombine p) {
 }
 int moe_combine(cudaStream_t st, int dtype, const MoeCombine &p, uint64_t *launches) {
   MX_DISPATCH(dtype, (moe_combine_kernel<T><<<dim3(p.M, p.M < 64 ? (p.W + 255) / 256 : 1), 256, 0, st>>>(p)));
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- block-wide sums
+// sums of up to two values over a CTA of up to 1024 threads; every thread receives the totals
+__device__ __forceinline__ void block_sum2(float &a, float &b, float *red /* [64] */) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();  // red may still be read from a previous use
+  if ((threadIdx.x & 31) == 0) { red[w] = a; red[32 + w] = b; }
+  __syncthreads();
+  float ta = 0.f, tb = 0.f;
+  for (int i = 0; i < nw; i++) { ta += red[i]; tb += red[32 + i]; }
+  a = ta;
+  b = tb;
+}
+
+// ---------------------------------------------------------------------------------------------- RMS norm of fp32 rows
+template <typename T>
+__global__ void __launch_bounds__(256) rms_rows_kernel(const RmsRows p) {
+  __shared__ float red[64];
+  const int m = blockIdx.x;
+  const float *x = p.x + (size_t)m * p.n;
+  const T *w = reinterpret_cast<const T *>(p.w);
+  float ss = 0.f, z = 0.f;
+  for (int i = threadIdx.x; i < p.n; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
+  block_sum2(ss, z, red);
+  const float inv = 1.0f / sqrtf(ss / (float)p.n + p.eps);
+  for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
+    const float v = x[i] * inv * (DT<T>::to_f(w[i]) + p.w_add);
+    if (p.out32) p.out32[(size_t)m * p.n + i] = v;
+    else reinterpret_cast<T *>(p.outD)[(size_t)m * p.n + i] = DT<T>::from_f(v);
+  }
+}
+int rms_rows(cudaStream_t st, int dtype, const RmsRows &p, uint64_t *launches) {
+  if (p.M < 1 || p.n < 1 || (!p.out32 && !p.outD)) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, (rms_rows_kernel<T><<<p.M, 256, 0, st>>>(p)));
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- h + conv(h) over time
+template <typename T>
+__global__ void __launch_bounds__(256) canon_conv_kernel(const CanonConv p) {
+  const int m = blockIdx.x, b = m / p.S, t = m % p.S, back = p.taps - 1;
+  const T *w = reinterpret_cast<const T *>(p.w);
+  const float *hist = p.hist + (size_t)b * back * p.n;
+  for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < p.n; ch += gridDim.y * blockDim.x) {
+    float acc = p.h[(size_t)m * p.n + ch];
+    for (int jt = 0; jt < p.taps; jt++) {
+      const int tt = t - back + jt;
+      float x = 0.f;
+      if (tt >= 0) x = p.h[((size_t)b * p.S + tt) * p.n + ch];
+      else if (p.pos0 > 0) x = hist[(size_t)(back + tt) * p.n + ch];
+      acc = fmaf(DT<T>::to_f(w[(size_t)ch * p.taps + jt]), x, acc);
+    }
+    reinterpret_cast<T *>(p.out)[(size_t)m * p.n + ch] = DT<T>::from_f(acc);
+  }
+}
+// afterwards: the history becomes the last taps - 1 inputs up to the end of this step (zeros before position 0)
+__global__ void canon_hist_kernel(const CanonConv p) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x, back = p.taps - 1;
+  if (idx >= p.B * p.n) return;
+  const int b = idx / p.n, ch = idx % p.n;
+  float *hist = p.hist + (size_t)b * back * p.n;
+  for (int jt = 0; jt < back; jt++) {  // ascending: an entry is read (at jt + S) before it is overwritten
+    const int tt = p.S - back + jt;
+    float v = 0.f;
+    if (tt >= 0) v = p.h[((size_t)b * p.S + tt) * p.n + ch];
+    else if (p.pos0 > 0) v = hist[(size_t)(jt + p.S) * p.n + ch];
+    hist[(size_t)jt * p.n + ch] = v;
+  }
+}
+int canon_conv(cudaStream_t st, int dtype, const CanonConv &p, uint64_t *launches) {
+  if (p.taps < 1 || p.B < 1 || p.S < 1) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, (canon_conv_kernel<T><<<dim3(p.B * p.S, (p.n + 255) / 256), 256, 0, st>>>(p)));
+  if (p.taps > 1) canon_hist_kernel<<<(p.B * p.n + 255) / 256, 256, 0, st>>>(p);
+  MX_DONE(p.taps > 1 ? 2 : 1);
+}
+
+// ---------------------------------------------------------------------------------------------- sublayer output -> stream
+template <typename T>
+__global__ void __launch_bounds__(256) branch_merge_kernel(const BranchMerge p) {
+  extern __shared__ float ys[];  // [n]
+  __shared__ float red[64];
+  const int m = blockIdx.x, n = p.n;
+  const float *a = p.a + (size_t)m * n, *b = p.b ? p.b + (size_t)m * n : nullptr;
+  const T *ba = reinterpret_cast<const T *>(p.a_bias), *bb = reinterpret_cast<const T *>(p.b_bias);
+  const T *wa = reinterpret_cast<const T *>(p.wa), *wb = reinterpret_cast<const T *>(p.wb), *post = reinterpret_cast<const T *>(p.post);
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float va = a[i] + (ba ? DT<T>::to_f(ba[i]) : 0.f);
+    ys[i] = va;
+    sa = fmaf(va, va, sa);
+    if (b) {
+      const float vb = b[i] + (bb ? DT<T>::to_f(bb[i]) : 0.f);
+      sb = fmaf(vb, vb, sb);
+    }
+  }
+  float sy = 0.f, z = 0.f;
+  if (b) {
+    block_sum2(sa, sb, red);
+    const float ia = 1.0f / sqrtf(sa / (float)n + p.eps), ib = 1.0f / sqrtf(sb / (float)n + p.eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {  // a thread revisits the entries it wrote
+      const float vb = b[i] + (bb ? DT<T>::to_f(bb[i]) : 0.f);
+      const float y = 0.5f * (ys[i] * ia * DT<T>::to_f(wa[i]) + vb * ib * DT<T>::to_f(wb[i]));
+      ys[i] = y;
+      sy = fmaf(y, y, sy);
+    }
+  } else sy = sa;
+  float iy = 1.f;
+  if (post) {
+    block_sum2(sy, z, red);
+    iy = 1.0f / sqrtf(sy / (float)n + p.eps);
+  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float y = post ? ys[i] * iy * (DT<T>::to_f(post[i]) + p.post_add) : ys[i];
+    p.x_out[(size_t)m * n + i] = p.x[(size_t)m * n + i] + y;
+  }
+}
+int branch_merge(cudaStream_t st, int dtype, const BranchMerge &p, uint64_t *launches) {
+  if (p.M < 1 || p.n < 1 || !p.a || (p.b && (!p.wa || !p.wb)) || (size_t)p.n * sizeof(float) > 200 * 1024) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)p.n * sizeof(float);
+  MX_DISPATCH(dtype, {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(branch_merge_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    branch_merge_kernel<T><<<p.M, 256, smem, st>>>(p);
+  });
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- gated delta rule
+template <typename T>
+__global__ void __launch_bounds__(128) delta_prep_kernel(const DeltaPrep p) {
+  const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int G = p.kv_heads, dk = p.dk;
+  for (int item = warp; item < 2 * G; item += nw) {
+    const int which = item / G, hd = item % G;
+    const T *src = reinterpret_cast<const T *>(which ? p.k : p.q) + (size_t)m * p.ld + (size_t)hd * dk;
+    float *dst = (which ? p.kn : p.qn) + (size_t)m * G * dk + (size_t)hd * dk;
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) {
+      const float v = DT<T>::to_f(src[i]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = (which ? 1.f : p.qscale) / sqrtf(ss + 1e-6f);
+    for (int i = lane; i < dk; i += 32) dst[i] = DT<T>::to_f(src[i]) * inv;
+  }
+  for (int h = threadIdx.x; h < p.heads; h += blockDim.x) {
+    const float br = DT<T>::to_f(reinterpret_cast<const T *>(p.braw)[(size_t)m * p.ldg + h]);
+    const float ar = DT<T>::to_f(reinterpret_cast<const T *>(p.araw)[(size_t)m * p.ldg + h]);
+    p.beta[(size_t)m * p.heads + h] = 1.0f / (1.0f + expf(-br));
+    const float rate = expf(DT<T>::to_f(reinterpret_cast<const T *>(p.a_log)[h]));
+    p.g[(size_t)m * p.heads + h] = expf(-rate * softplus_f(ar + DT<T>::to_f(reinterpret_cast<const T *>(p.dt_bias)[h])));
+  }
+}
+int delta_prep(cudaStream_t st, int dtype, const DeltaPrep &p, uint64_t *launches) {
+  if (p.M < 1 || p.heads < 1 || p.kv_heads < 1 || p.dk < 1) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, (delta_prep_kernel<T><<<p.M, 128, 0, st>>>(p)));
+  MX_DONE(1);
+}
+
+// A thread owns one column of the state (dk values): the columns are independent, u and o of a column need only that column.
+// DKP > 0: the column sits in DKP registers (dk <= DKP, the rest zero); DKP == 0: in shared memory, any dk.  Tokens come in
+// chunks of DR_TT whose q, k, v, beta and g are staged in shared memory once per CTA (blockDim.x columns of one head).
+constexpr int DR_TT = 16;
+template <typename T, int DKP>
+__global__ void __launch_bounds__(128) delta_rule_kernel(const DeltaRule p) {
+  extern __shared__ float sm[];
+  const int CB = blockDim.x, dk = p.dk, dv = p.dv;
+  const int ld = DKP > 0 ? DKP : (dk + 3) / 4 * 4;   // row length of the staged q / k
+  float *qs = sm, *ks = qs + DR_TT * ld, *vs = ks + DR_TT * ld, *gs = vs + DR_TT * CB, *bs = gs + DR_TT, *Ss = bs + DR_TT;
+  const int ncb = (dv + CB - 1) / CB, h = blockIdx.x / ncb, cb = blockIdx.x % ncb, b = blockIdx.y;
+  const int col = cb * CB + threadIdx.x;
+  const bool active = col < dv;
+  const int kvh = h / (p.heads / p.kv_heads), qk_ld = p.kv_heads * dk;
+  float *gstate = p.state + ((size_t)b * p.heads + h) * dk * dv + col;
+  float St[DKP > 0 ? DKP : 1];
+  if (DKP > 0) {
+#pragma unroll
+    for (int r = 0; r < DKP; r++) St[r] = (active && r < dk && p.pos0 > 0) ? gstate[(size_t)r * dv] : 0.f;
+  } else {
+    for (int r = 0; r < dk; r++) Ss[r * CB + threadIdx.x] = (active && p.pos0 > 0) ? gstate[(size_t)r * dv] : 0.f;
+  }
+  for (int t0 = 0; t0 < p.S; t0 += DR_TT) {
+    const int nt = min(DR_TT, p.S - t0);
+    const size_t m0 = (size_t)b * p.S + t0;
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * ld; idx += CB) {
+      const int tt = idx / ld, r = idx % ld;
+      qs[idx] = r < dk ? p.qn[(m0 + tt) * qk_ld + (size_t)kvh * dk + r] : 0.f;
+      ks[idx] = r < dk ? p.kn[(m0 + tt) * qk_ld + (size_t)kvh * dk + r] : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < nt * CB; idx += CB) {
+      const int tt = idx / CB, j = cb * CB + idx % CB;
+      vs[idx] = j < dv ? DT<T>::to_f(reinterpret_cast<const T *>(p.v)[(m0 + tt) * p.ldv + (size_t)h * dv + j]) : 0.f;
+    }
+    if ((int)threadIdx.x < nt) {
+      gs[threadIdx.x] = p.g[(m0 + threadIdx.x) * p.heads + h];
+      bs[threadIdx.x] = p.beta[(m0 + threadIdx.x) * p.heads + h];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; tt++) {
+      const float g = gs[tt];
+      const float *kq = ks + tt * ld, *qq = qs + tt * ld;
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      if (DKP > 0) {
+#pragma unroll
+        for (int r = 0; r < DKP; r += 4) {
+          const float4 k4 = *reinterpret_cast<const float4 *>(kq + r);
+          St[r] *= g; d0 = fmaf(St[r], k4.x, d0);
+          St[r + 1] *= g; d1 = fmaf(St[r + 1], k4.y, d1);
+          St[r + 2] *= g; d2 = fmaf(St[r + 2], k4.z, d2);
+          St[r + 3] *= g; d3 = fmaf(St[r + 3], k4.w, d3);
+        }
+      } else {
+        for (int r = 0; r < dk; r++) {
+          const float sv = Ss[r * CB + threadIdx.x] * g;
+          Ss[r * CB + threadIdx.x] = sv;
+          d0 = fmaf(sv, kq[r], d0);
+        }
+      }
+      const float u = bs[tt] * (vs[tt * CB + threadIdx.x] - ((d0 + d1) + (d2 + d3)));
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      if (DKP > 0) {
+#pragma unroll
+        for (int r = 0; r < DKP; r += 4) {
+          const float4 k4 = *reinterpret_cast<const float4 *>(kq + r), q4 = *reinterpret_cast<const float4 *>(qq + r);
+          St[r] = fmaf(k4.x, u, St[r]); o0 = fmaf(St[r], q4.x, o0);
+          St[r + 1] = fmaf(k4.y, u, St[r + 1]); o1 = fmaf(St[r + 1], q4.y, o1);
+          St[r + 2] = fmaf(k4.z, u, St[r + 2]); o2 = fmaf(St[r + 2], q4.z, o2);
+          St[r + 3] = fmaf(k4.w, u, St[r + 3]); o3 = fmaf(St[r + 3], q4.w, o3);
+        }
+      } else {
+        for (int r = 0; r < dk; r++) {
+          const float sv = fmaf(kq[r], u, Ss[r * CB + threadIdx.x]);
+          Ss[r * CB + threadIdx.x] = sv;
+          o0 = fmaf(sv, qq[r], o0);
+        }
+      }
+      if (active) p.o[(m0 + tt) * ((size_t)p.heads * dv) + (size_t)h * dv + col] = (o0 + o1) + (o2 + o3);
+    }
+  }
+  if (active) {
+    if (DKP > 0) {
+#pragma unroll
+      for (int r = 0; r < DKP; r++)
+        if (r < dk) gstate[(size_t)r * dv] = St[r];
+    } else {
+      for (int r = 0; r < dk; r++) gstate[(size_t)r * dv] = Ss[r * CB + threadIdx.x];
+    }
+  }
+}
+template <typename T, int DKP> static cudaError_t launch_delta_rule(cudaStream_t st, const DeltaRule &p) {
+  // columns per CTA: 64 when that still gives every SM a CTA, else 32
+  int CB = (p.dv % 64 == 0 && (long)p.B * p.heads * (p.dv / 64) >= 148) ? 64 : 32;
+  const int ld = DKP > 0 ? DKP : (p.dk + 3) / 4 * 4;
+  const size_t smem = ((size_t)2 * DR_TT * ld + (size_t)DR_TT * CB + 2 * DR_TT + (DKP > 0 ? 0 : (size_t)p.dk * CB)) * sizeof(float);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<T, DKP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  delta_rule_kernel<T, DKP><<<dim3(p.heads * ((p.dv + CB - 1) / CB), p.B), CB, smem, st>>>(p);
+  return cudaSuccess;
+}
+int delta_rule(cudaStream_t st, int dtype, const DeltaRule &p, uint64_t *launches) {
+  if (p.B < 1 || p.S < 1 || p.heads < 1 || p.kv_heads < 1 || p.heads % p.kv_heads || p.dk < 1 || p.dv < 1) return (int)cudaErrorInvalidValue;
+  cudaError_t e = cudaSuccess;
+  MX_DISPATCH(dtype, {
+    if (p.dk <= 16) e = launch_delta_rule<T, 16>(st, p);
+    else if (p.dk <= 32) e = launch_delta_rule<T, 32>(st, p);
+    else if (p.dk <= 64) e = launch_delta_rule<T, 64>(st, p);
+    else if (p.dk <= 96) e = launch_delta_rule<T, 96>(st, p);
+    else if (p.dk <= 128) e = launch_delta_rule<T, 128>(st, p);
+    else e = launch_delta_rule<T, 0>(st, p);
+  });
+  if (e != cudaSuccess) return (int)e;
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- exponential gates
+// One warp per (head, batch row) walks the tokens in order; lane l owns the entries l, l + 32, ... of the normaliser n.
+constexpr int GP_TT = 16;
+template <typename T>
+__global__ void __launch_bounds__(32) gate_prep_kernel(const GatePrep p) {
+  extern __shared__ float sm[];
+  const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x, dk = p.dk;
+  float *ns = sm, *ks = ns + dk, *qs = ks + GP_TT * dk, *lis = qs + GP_TT * dk, *lfs = lis + GP_TT;
+  float *aux = p.aux + ((size_t)b * p.heads + h) * (dk + 1);
+  for (int r = lane; r < dk; r += 32) ns[r] = p.pos0 > 0 ? aux[r] : 0.f;
+  float mx = p.pos0 > 0 ? aux[dk] : 0.f;
+  const float ib = DT<T>::to_f(reinterpret_cast<const T *>(p.i_b)[h]), fb = DT<T>::to_f(reinterpret_cast<const T *>(p.f_b)[h]);
+  for (int t0 = 0; t0 < p.S; t0 += GP_TT) {
+    const int nt = min(GP_TT, p.S - t0);
+    const size_t m0 = (size_t)b * p.S + t0;
+    __syncwarp();
+    for (int idx = lane; idx < nt * dk; idx += 32) {
+      const int tt = idx / dk, r = idx % dk;
+      ks[idx] = DT<T>::to_f(reinterpret_cast<const T *>(p.k)[(m0 + tt) * p.ld + (size_t)h * dk + r]);
+      qs[idx] = DT<T>::to_f(reinterpret_cast<const T *>(p.q)[(m0 + tt) * p.ld + (size_t)h * dk + r]);
+    }
+    if (lane < nt) {
+      const float ir = DT<T>::to_f(reinterpret_cast<const T *>(p.iraw)[(m0 + lane) * p.ldg + h]) + ib;
+      const float fr = DT<T>::to_f(reinterpret_cast<const T *>(p.fraw)[(m0 + lane) * p.ldg + h]) + fb;
+      lis[lane] = p.cap * tanhf(ir / p.cap);
+      const float z = p.cap * tanhf(fr / p.cap);
+      lfs[lane] = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));  // log sigmoid(z)
+    }
+    __syncwarp();
+    for (int tt = 0; tt < nt; tt++) {
+      const float li = lis[tt], lf = lfs[tt];
+      const float mn = fmaxf(lf + mx, li);
+      const float a = expf(lf + mx - mn), bb = expf(li - mn);
+      float dot = 0.f;
+      for (int r = lane; r < dk; r += 32) {
+        const float nv = fmaf(a, ns[r], bb * ks[tt * dk + r]);
+        ns[r] = nv;
+        dot = fmaf(nv, qs[tt * dk + r], dot);
+      }
+      dot = warp_sum(dot) * p.qscale;
+      if (lane == 0) {
+        const size_t o = (m0 + tt) * p.heads + h;
+        p.a[o] = a;
+        p.b[o] = bb;
+        p.div[o] = (fmaxf(fabsf(dot), expf(-mn)) + 1e-6f) / p.qscale;
+      }
+      mx = mn;
+    }
+  }
+  __syncwarp();
+  for (int r = lane; r < dk; r += 32) aux[r] = ns[r];
+  if (lane == 0) aux[dk] = mx;
+}
+int gate_prep(cudaStream_t st, int dtype, const GatePrep &p, uint64_t *launches) {
+  if (p.B < 1 || p.S < 1 || p.heads < 1 || p.dk < 1 || !(p.cap > 0.f) || !(p.qscale > 0.f)) return (int)cudaErrorInvalidValue;
+  const size_t smem = ((size_t)p.dk * (1 + 2 * GP_TT) + 2 * GP_TT) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(gate_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    gate_prep_kernel<T><<<dim3(p.heads, p.B), 32, smem, st>>>(p);
+  });
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- attention with mixed heads
+// Scores of one key against up to eight query heads of its kv head: acc[i] = q_i . k
+template <typename T>
+__device__ __forceinline__ void key_scores8(const T *__restrict__ krow, const float *__restrict__ q, int ng, int dim, float (&acc)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i] = 0.f;
+  if (sizeof(T) == 2 && (dim & 7) == 0 && ((uintptr_t)krow & 15) == 0) {
+    typedef typename Bits16<T>::type B;
+    for (int d = 0; d < dim; d += 8) {
+      float kf[8];
+      unpack8<B>(*reinterpret_cast<const uint4 *>(krow + d), kf);
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        if (i < ng) {
+          const float4 qa = *reinterpret_cast<const float4 *>(q + i * dim + d), qb = *reinterpret_cast<const float4 *>(q + i * dim + d + 4);
+          float s = acc[i];
+          s = fmaf(kf[0], qa.x, s); s = fmaf(kf[1], qa.y, s); s = fmaf(kf[2], qa.z, s); s = fmaf(kf[3], qa.w, s);
+          s = fmaf(kf[4], qb.x, s); s = fmaf(kf[5], qb.y, s); s = fmaf(kf[6], qb.z, s); s = fmaf(kf[7], qb.w, s);
+          acc[i] = s;
+        }
+    }
+    return;
+  }
+  for (int d = 0; d < dim; d++) {
+    const float kv = DT<T>::to_f(krow[d]);
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+      if (i < ng) acc[i] = fmaf(kv, q[i * dim + d], acc[i]);
+  }
+}
+
+// One CTA per query row (and per key range when the keys are split), all heads.  Pass 1: every thread keeps a running
+// (max, sum) per head over its keys, merged per head at the end.  Pass 2: the scores are computed again, normalised, mixed
+// across heads, and a tile of mixed weights in shared memory is applied to the values by threads that own output entries.
+// PHASE 0: both passes in one kernel.  PHASE 1 / 2: the passes of the split form (stats of a key range -> part; the second
+// pass merges the ranges' stats itself and leaves partial outputs in part).
+constexpr int TA_MAXO = 16;
+template <typename T, int PHASE>
+__global__ void __launch_bounds__(256) talk_attn_kernel(const TalkAttn p) {
+  extern __shared__ float sm[];
+  const int NT = blockDim.x, H = p.heads, G = p.kv_heads, dim = p.dim, vdim = p.vdim, grp = H / G;
+  float *qs = sm, *M_ = qs + (size_t)H * dim, *L_ = M_ + H, *tk = L_ + H, *ta = tk + H * H, *tb = ta + (size_t)H * NT;
+  const int m = blockIdx.x, b = m / p.S, t = m % p.S, pos = p.pos0 + t, nk_all = pos + 1;
+  const int ns = PHASE == 0 ? 1 : p.nsplit, sp = PHASE == 0 ? 0 : blockIdx.y;
+  const int per = (nk_all + ns - 1) / ns, k_lo = sp * per, k_hi = min(nk_all, k_lo + per);
+  const T *kc = reinterpret_cast<const T *>(p.kc) + (size_t)b * G * p.cap * dim;
+  const T *vc = reinterpret_cast<const T *>(p.vc) + (size_t)b * G * p.cap * vdim;
+  for (int i = threadIdx.x; i < H * dim; i += NT) qs[i] = DT<T>::to_f(reinterpret_cast<const T *>(p.q)[(size_t)m * p.ldq + i]);
+  if (p.talk)
+    for (int i = threadIdx.x; i < H * H; i += NT) tk[i] = DT<T>::to_f(reinterpret_cast<const T *>(p.talk)[i]);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = NT >> 5;
+  auto score_all = [&](int j, float *dst /* dst[g * NT + tid] */) {
+    const int dist = min(pos - j, p.bias_len - 1);
+    for (int c = 0; c < G; c++) {
+      const T *krow = kc + ((size_t)c * p.cap + j) * dim;
+      for (int g0 = 0; g0 < grp; g0 += 8) {
+        const int ng = min(8, grp - g0), gb = c * grp + g0;
+        float acc[8];
+        key_scores8<T>(krow, qs + (size_t)gb * dim, ng, dim, acc);
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+          if (i < ng) dst[(size_t)(gb + i) * NT + threadIdx.x] = fmaf(acc[i], p.scale, p.bias ? p.bias[(size_t)dist * H + gb + i] : 0.f);
+      }
+    }
+  };
+  if (PHASE != 2) {
+    for (int g = 0; g < H; g++) { ta[(size_t)g * NT + threadIdx.x] = -INFINITY; tb[(size_t)g * NT + threadIdx.x] = 0.f; }
+    __syncthreads();  // qs
+    // running (max, sum) per head of this thread's keys; the fresh scores pass through the first H entries of sc
+    for (int j = k_lo + threadIdx.x; j < k_hi; j += NT) {
+      const int dist = min(pos - j, p.bias_len - 1);
+      for (int c = 0; c < G; c++) {
+        const T *krow = kc + ((size_t)c * p.cap + j) * dim;
+        for (int g0 = 0; g0 < grp; g0 += 8) {
+          const int ng = min(8, grp - g0), gb = c * grp + g0;
+          float acc[8];
+          key_scores8<T>(krow, qs + (size_t)gb * dim, ng, dim, acc);
+#pragma unroll
+          for (int i = 0; i < 8; i++)
+            if (i < ng) {
+              const float s = fmaf(acc[i], p.scale, p.bias ? p.bias[(size_t)dist * H + gb + i] : 0.f);
+              const size_t o = (size_t)(gb + i) * NT + threadIdx.x;
+              const float mo = ta[o], mn = fmaxf(mo, s);
+              tb[o] = tb[o] * expf(mo - mn) + expf(s - mn);  // exp(-inf) = 0 on the first key
+              ta[o] = mn;
+            }
+        }
+      }
+    }
+    __syncthreads();
+    for (int g = warp; g < H; g += nw) {  // merge the threads' pairs of head g
+      float mx = -INFINITY;
+      for (int i = lane; i < NT; i += 32) mx = fmaxf(mx, ta[(size_t)g * NT + i]);
+      mx = warp_max(mx);
+      float l = 0.f;
+      for (int i = lane; i < NT; i += 32) {
+        const float mi = ta[(size_t)g * NT + i];
+        if (mi > -INFINITY) l += tb[(size_t)g * NT + i] * expf(mi - mx);
+      }
+      l = warp_sum(l);
+      if (lane == 0) {
+        if (PHASE == 1) {
+          float *st = p.part + (((size_t)m * ns + sp) * H + g) * 2;
+          st[0] = mx;
+          st[1] = l;
+        } else { M_[g] = mx; L_[g] = l; }
+      }
+    }
+    if (PHASE == 1) return;
+    __syncthreads();
+  } else {
+    for (int g = threadIdx.x; g < H; g += NT) {  // merge the key ranges' stats
+      float mx = -INFINITY;
+      for (int s2 = 0; s2 < ns; s2++) mx = fmaxf(mx, p.part[(((size_t)m * ns + s2) * H + g) * 2]);
+      float l = 0.f;
+      for (int s2 = 0; s2 < ns; s2++) {
+        const float *st = p.part + (((size_t)m * ns + s2) * H + g) * 2;
+        if (st[0] > -INFINITY) l += st[1] * expf(st[0] - mx);
+      }
+      M_[g] = mx;
+      L_[g] = l;
+    }
+    __syncthreads();
+  }
+  // pass 2, once per TA_MAXO * NT output entries (one round unless heads * vdim exceeds that)
+  const int n_out = H * vdim;
+  for (int o0 = 0; o0 < n_out; o0 += TA_MAXO * NT) {
+  float acc[TA_MAXO];
+#pragma unroll
+  for (int k = 0; k < TA_MAXO; k++) acc[k] = 0.f;
+  for (int j0 = k_lo; j0 < k_hi; j0 += NT) {
+    const int j = j0 + threadIdx.x, nj = min(NT, k_hi - j0);
+    if (j < k_hi) {
+      score_all(j, ta);
+      for (int g = 0; g < H; g++) ta[(size_t)g * NT + threadIdx.x] = expf(ta[(size_t)g * NT + threadIdx.x] - M_[g]) / L_[g];
+      if (p.talk)
+        for (int hh = 0; hh < H; hh++) {
+          float w = 0.f;
+          for (int g = 0; g < H; g++) w = fmaf(tk[hh * H + g], ta[(size_t)g * NT + threadIdx.x], w);
+          tb[(size_t)hh * NT + threadIdx.x] = w;
+        }
+    }
+    __syncthreads();
+    const float *wt = p.talk ? tb : ta;
+#pragma unroll
+    for (int k = 0; k < TA_MAXO; k++) {
+      const int idx = o0 + threadIdx.x + k * NT;
+      if (idx < n_out) {
+        const int hh = idx / vdim, e = idx % vdim;
+        const T *vcol = vc + ((size_t)(hh / grp) * p.cap + j0) * vdim + e;
+        const float *wrow = wt + (size_t)hh * NT;
+        float a = acc[k];
+        for (int jj = 0; jj < nj; jj++) a = fmaf(wrow[jj], DT<T>::to_f(vcol[(size_t)jj * vdim]), a);
+        acc[k] = a;
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int k = 0; k < TA_MAXO; k++) {
+    const int idx = o0 + threadIdx.x + k * NT;
+    if (idx < n_out) {
+      if (PHASE == 2) {
+        p.part[(size_t)p.B * p.S * ns * H * 2 + ((size_t)m * ns + sp) * n_out + idx] = acc[k];
+      } else {
+        float o = acc[k];
+        if (p.gate) o *= 1.0f / (1.0f + expf(-DT<T>::to_f(reinterpret_cast<const T *>(p.gate)[(size_t)m * p.ldg + idx])));
+        reinterpret_cast<T *>(p.out)[(size_t)m * n_out + idx] = DT<T>::from_f(o);
+      }
+    }
+  }
+  }
+}
+// the split form's last step: the key ranges' partial outputs are added in range order, gated and stored in D
+template <typename T>
+__global__ void __launch_bounds__(256) talk_attn_merge_kernel(const TalkAttn p) {
+  const int m = blockIdx.x, n_out = p.heads * p.vdim, ns = p.nsplit;
+  const float *part = p.part + (size_t)p.B * p.S * ns * p.heads * 2 + (size_t)m * ns * n_out;
+  for (int idx = threadIdx.x; idx < n_out; idx += blockDim.x) {
+    float o = 0.f;
+    for (int s2 = 0; s2 < ns; s2++) o += part[(size_t)s2 * n_out + idx];
+    if (p.gate) o *= 1.0f / (1.0f + expf(-DT<T>::to_f(reinterpret_cast<const T *>(p.gate)[(size_t)m * p.ldg + idx])));
+    reinterpret_cast<T *>(p.out)[(size_t)m * n_out + idx] = DT<T>::from_f(o);
+  }
+}
+int talk_attention(cudaStream_t st, int dtype, const TalkAttn &p, uint64_t *launches) {
+  if (p.B < 1 || p.S < 1 || p.heads < 1 || p.kv_heads < 1 || p.heads % p.kv_heads || p.dim < 1 || p.vdim < 1 || (p.bias && p.bias_len < 1))
+    return (int)cudaErrorInvalidValue;
+  const int NT = 256;
+  const size_t smem = ((size_t)p.heads * p.dim + 2 * p.heads + (size_t)p.heads * p.heads + 2 * (size_t)p.heads * NT) * sizeof(float);
+  if (smem > 220 * 1024) return (int)cudaErrorInvalidValue;
+  const int M = p.B * p.S;
+  const bool split = p.part && p.nsplit > 1;
+  MX_DISPATCH(dtype, {
+    cudaError_t e = cudaSuccess;
+    if (smem > 48 * 1024) {
+      e = cudaFuncSetAttribute(talk_attn_kernel<T, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(talk_attn_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(talk_attn_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    if (!split) talk_attn_kernel<T, 0><<<M, NT, smem, st>>>(p);
+    else {
+      talk_attn_kernel<T, 1><<<dim3(M, p.nsplit), NT, smem, st>>>(p);
+      talk_attn_kernel<T, 2><<<dim3(M, p.nsplit), NT, smem, st>>>(p);
+      talk_attn_merge_kernel<T><<<M, 256, 0, st>>>(p);
+    }
+  });
+  MX_DONE(split ? 3 : 1);
+}
+
+template <typename T>
+__global__ void distance_bias_kernel(const T *__restrict__ rel, const int *__restrict__ bucket, float *__restrict__ bias, int len, int heads) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= len * heads) return;
+  bias[idx] = DT<T>::to_f(rel[(size_t)bucket[idx / heads] * heads + idx % heads]);
+}
+int distance_bias_table(cudaStream_t st, int dtype, const void *rel, const int *bucket, float *bias, int len, int heads, uint64_t *launches) {
+  if (len < 1 || heads < 1) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, (distance_bias_kernel<T><<<(len * heads + 255) / 256, 256, 0, st>>>(reinterpret_cast<const T *>(rel), bucket, bias, len, heads)));
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- embedding with tables
+template <typename T>
+__global__ void __launch_bounds__(128) embed_tables_kernel(const EmbedTables p) {
+  const int r = blockIdx.x, b = r / p.S, t = r % p.S;
+  uint32_t id = p.ids[r];
+  if (id >= (uint32_t)p.vocab) id = 0;
+  const T *E = reinterpret_cast<const T *>(p.E) + (size_t)id * p.W;
+  const T *bg = nullptr, *ps = nullptr;
+  if (p.bigram) {
+    long long row = p.buckets;  // a sequence's first token
+    if (t > 0 || p.pos0 > 0) {
+      const long long prev = t > 0 ? p.ids[r - 1] : p.ids[(size_t)p.B * p.S + b];
+      row = (prev * (long long)p.mul_prev + (long long)id * p.mul_cur) % p.buckets;
+    }
+    bg = reinterpret_cast<const T *>(p.bigram) + (size_t)row * p.W;
+  }
+  if (p.pos) ps = reinterpret_cast<const T *>(p.pos) + (size_t)(p.pos0 + t) * p.W;
+  for (int i = threadIdx.x; i < p.W; i += blockDim.x) {
+    float v = DT<T>::to_f(E[i]);
+    if (p.scale != 0.f) v *= p.scale;
+    if (bg) v += DT<T>::to_f(bg[i]);
+    if (ps) v += DT<T>::to_f(ps[i]);
+    p.x[(size_t)r * p.W + i] = v;
+  }
+}
+int embed_tables(cudaStream_t st, int dtype, const EmbedTables &p, uint64_t *launches) {
+  if (p.B < 1 || p.S < 1 || (p.bigram && p.buckets < 1)) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, (embed_tables_kernel<T><<<p.B * p.S, 128, 0, st>>>(p)));
   MX_DONE(1);
 }
 

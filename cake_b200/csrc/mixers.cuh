@@ -93,6 +93,8 @@ struct Recurrence {
   float *state;          // [B, heads, dk, dv]
   float *o;              // [M, heads * dv] fp32
   int B, S, heads, dk, dv, pos0;
+  // per-token factors computed elsewhere: a_t = a_tok[m, h], b_t = b_tok[m, h] (fp32 [M, heads]); they override decay / dt
+  const float *a_tok = nullptr, *b_tok = nullptr;
 };
 int recurrence(cudaStream_t, int dtype, const Recurrence &, uint64_t *launches);
 
@@ -100,7 +102,7 @@ int recurrence(cudaStream_t, int dtype, const Recurrence &, uint64_t *launches);
 struct ShortConv {
   const void *in;        // [M, ld] D, channels from column col0
   int ld, col0;
-  const void *w, *bias;  // [channels, taps] (last tap = current token), [channels] D
+  const void *w, *bias;  // [channels, taps] (last tap = current token), [channels] D (bias may be nullptr)
   void *hist;            // [B, taps - 1, channels] D: the inputs before the step; updated to the step's last ones
   void *out;             // [M, channels] D
   int B, S, channels, taps, pos0;
@@ -117,6 +119,9 @@ struct GateNorm {
   void *out;             // [M, n] D
   int M, n, parts, gate_first;
   float eps;
+  int gate_sigmoid = 0;            // 1: the gate is sigmoid(gate) instead of silu(gate)
+  int w_period = 0;                // > 0: w has w_period entries and repeats (one gain vector shared by every part)
+  const float *row_div = nullptr;  // [M, parts] fp32: o of a part is divided by its entry before anything else
 };
 int gate_norm(cudaStream_t, int dtype, const GateNorm &, uint64_t *launches);
 
@@ -169,6 +174,124 @@ struct MoeCombine {
   int M, W, top, experts;
 };
 int moe_combine(cudaStream_t, int dtype, const MoeCombine &, uint64_t *launches);
+
+// ---- RMS norm of rows of the fp32 stream, gain = w + w_add --------------------------------------------------------------
+struct RmsRows {
+  const float *x;        // [M, n] fp32
+  const void *w;         // [n] D
+  float w_add;
+  float *out32;          // one of the two outputs: [M, n] fp32 ...
+  void *outD;            // ... or [M, n] D
+  int M, n;
+  float eps;
+};
+int rms_rows(cudaStream_t, int dtype, const RmsRows &, uint64_t *launches);
+
+// ---- h + conv(h): causal convolution over time per channel of an fp32 activation, no bias, no activation -----------------
+struct CanonConv {
+  const float *h;        // [M, n] fp32
+  const void *w;         // [n, taps] D, last tap = the current token
+  float *hist;           // [B, taps - 1, n] fp32: the inputs before the step; updated to the step's last ones
+  void *out;             // [M, n] D
+  int B, S, n, taps, pos0;
+};
+int canon_conv(cudaStream_t, int dtype, const CanonConv &, uint64_t *launches);
+
+// ---- sublayer output -> residual stream -----------------------------------------------------------------------------------
+//   one branch:   y = a + a_bias
+//   two branches: y = ( rms(a + a_bias) * wa + rms(b + b_bias) * wb ) / 2        (rms over the row, plain gains)
+//   x_out = x + (post ? rms(y) * (post + post_add) : y)
+struct BranchMerge {
+  const float *a, *b;    // [M, n] fp32; b may be nullptr
+  const void *a_bias, *b_bias, *wa, *wb, *post;  // [n] D, nullable (wa / wb: required with two branches)
+  float post_add;
+  const float *x;
+  float *x_out;          // may alias x
+  int M, n;
+  float eps;
+};
+int branch_merge(cudaStream_t, int dtype, const BranchMerge &, uint64_t *launches);
+
+// ---- gated delta rule -----------------------------------------------------------------------------------------------------
+// Prep: q and k of every key head become unit vectors (x / sqrt(sum x^2 + 1e-6); q also times qscale) in fp32, and per head
+// beta = sigmoid(braw), g = exp(-exp(a_log[h]) * softplus(araw + dt_bias[h])).
+struct DeltaPrep {
+  const void *q, *k;     // [M, ld] D (after convolution and silu), kv_heads * dk entries each
+  int ld;
+  const void *braw, *araw;  // [M, ldg] D, heads entries each
+  int ldg;
+  const void *a_log, *dt_bias;  // [heads] D
+  float *qn, *kn;        // [M, kv_heads * dk] fp32
+  float *beta, *g;       // [M, heads] fp32
+  int M, heads, kv_heads, dk;
+  float qscale;
+};
+int delta_prep(cudaStream_t, int dtype, const DeltaPrep &, uint64_t *launches);
+// S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q     (S: [dk, dv] fp32 per batch row and head)
+struct DeltaRule {
+  const float *qn, *kn;  // [M, kv_heads * dk] fp32
+  const void *v;         // [M, ldv] D, heads * dv entries
+  int ldv;
+  const float *beta, *g; // [M, heads]
+  float *state;          // [B, heads, dk, dv]; read unless pos0 == 0, written back at the end
+  float *o;              // [M, heads * dv] fp32
+  int B, S, heads, kv_heads, dk, dv, pos0;
+};
+int delta_rule(cudaStream_t, int dtype, const DeltaRule &, uint64_t *launches);
+
+// ---- exponential gates of a matrix memory -----------------------------------------------------------------------------------
+// Per (batch row, head), in token order: li = cap tanh((iraw + i_b) / cap), lf = logsigmoid(cap tanh((fraw + f_b) / cap)),
+// m' = max(lf + m, li), a = exp(lf + m - m'), b = exp(li - m'), n <- a n + b k, div = (max(|qscale n . q|, exp(-m')) + 1e-6) / qscale.
+// a and b drive `recurrence` (S <- a S + b k v^T, o = S^T q); o / div is the read-out.  aux = [n (dk) | m] per (batch row, head).
+struct GatePrep {
+  const void *q, *k;     // [M, ld] D, heads * dk entries each
+  int ld;
+  const void *iraw, *fraw;  // [M, ldg] D, heads entries each
+  int ldg;
+  const void *i_b, *f_b; // [heads] D
+  float *aux;            // [B, heads, dk + 1] fp32; read unless pos0 == 0
+  float *a, *b, *div;    // [M, heads] fp32
+  int B, S, heads, dk, pos0;
+  float cap, qscale;
+};
+int gate_prep(cudaStream_t, int dtype, const GatePrep &, uint64_t *launches);
+
+// ---- softmax attention whose heads' weights are mixed after the softmax ----------------------------------------------------
+//   s_g(i, j) = (q_g(i) . k_c(g)(j)) * scale + bias[i - j, g]     for j <= i, c(g) = g / (heads / kv_heads)
+//   w_g = softmax_j s_g;   w'_h = sum_g talk[h, g] w_g   (talk == nullptr: w' = w);   o_h(i) = sum_j w'_h(i, j) v_c(h)(j)
+//   out = o * sigmoid(gate)  (gate == nullptr: o)
+struct TalkAttn {
+  const void *q;         // [M, ldq] D, heads * dim entries
+  int ldq;
+  const void *kc, *vc;   // [B, kv_heads, cap, dim], [B, kv_heads, cap, vdim] D; positions 0 .. pos0 + S - 1 are valid
+  const void *gate;      // [M, ldg] D, heads * vdim entries, or nullptr
+  int ldg;
+  const float *bias;     // [bias_len, heads] fp32 by distance (distances >= bias_len read the last row), or nullptr
+  int bias_len;
+  const void *talk;      // [heads, heads] D or nullptr
+  void *out;             // [M, heads * vdim] D
+  int B, S, heads, kv_heads, dim, vdim, cap, pos0;
+  float scale;
+  // steps of a few rows over many keys: the keys are split over nsplit CTAs per row; part holds
+  // [M, nsplit, heads, 2] running (max, sum) and then [M, nsplit, heads * vdim] partial outputs (fp32)
+  float *part = nullptr;
+  int nsplit = 0;
+};
+int talk_attention(cudaStream_t, int dtype, const TalkAttn &, uint64_t *launches);
+// bias[d, h] = rel[bucket[d], h] for d < len (bucket: device ints): the per-distance form TalkAttn reads
+int distance_bias_table(cudaStream_t, int dtype, const void *rel, const int *bucket, float *bias, int len, int heads, uint64_t *launches);
+
+// ---- x[t] = E[id] * scale + bigram[(prev * mul_prev + id * mul_cur) mod buckets  |  buckets for a first token] + pos[p] ------
+struct EmbedTables {
+  const void *E;         // [vocab, W] D
+  const uint32_t *ids;   // [B * S] then [B] previous tokens of every batch row's first token (ignored when pos0 == 0)
+  const void *bigram;    // [buckets + 1, W] D or nullptr
+  const void *pos;       // [positions, W] D or nullptr
+  float *x;              // [B * S, W] fp32
+  int B, S, W, vocab, buckets, mul_prev, mul_cur, pos0;
+  float scale;           // 0 = none
+};
+int embed_tables(cudaStream_t, int dtype, const EmbedTables &, uint64_t *launches);
 
 // ---- x[m] += (x0 ? x0[m] : 0) + vec   (fp32 stream; vec [W] in D) --------------------------------------------------------
 int stream_inject(cudaStream_t, int dtype, float *x, const float *x0, const void *vec, int M, int W, uint64_t *launches);

@@ -345,6 +345,58 @@ def mixer_block_tensors(vb, cfg: Config, index: int) -> Dict[str, object]:
     return out
 
 
+def nuvarax_block_tensors(vb, cfg: Config, index: int):
+    """The tensors of layer ``index`` of a Nuvarax checkpoint by the field names of ``cake_b200_mixer_tensors``: (main, side or
+    None), each checked against the shape its MixerSpec declares.  Names under ``l<i>.``: ``norm1``, ``norm1b``, ``norm2``,
+    ``norm2b``, ``canon1``, ``mlp.{gate,up,down}`` and ``mix.*``: a delta layer has ``q, k, v`` (+ ``.conv``), ``b``, ``a``, ``A_log``,
+    ``dt_bias``, ``norm``, ``g``, ``o``; a parallel layer ``left.{q,k,v,o}`` (+ ``.b``), ``left.{rel,talk,g,out}`` and
+    ``right.{q,k,v,g,o,norm,out}``, ``right.{i,f}`` (+ ``.b``).  The rows of ``rel`` set the spec's ``bias_rows``."""
+    sp, H, name = cfg.layers[index], cfg.hidden_size, cfg.layer_name(index)
+
+    def get(short, shape):
+        t = vb.get(f"{name}.{short}")
+        if t is None:
+            raise KeyError(f"tensor {name}.{short} not found")
+        if tuple(t.shape) != tuple(shape):
+            raise ValueError(f"shape mismatch for {name}.{short}, expected: {list(shape)}, got: {list(t.shape)}")
+        return t
+
+    main = {"norm1": get("norm1", (H,))}
+    if sp.post_norms:
+        main["post1"] = get("norm1b", (H,))
+    if sp.canon_taps > 1:
+        main["canon"] = get("canon1", (H, sp.canon_taps))
+    if sp.dense_ff:
+        main.update(norm2=get("norm2", (H,)), ff_gate=get("mlp.gate", (sp.dense_ff, H)), ff_up=get("mlp.up", (sp.dense_ff, H)),
+                    ff_down=get("mlp.down", (H, sp.dense_ff)))
+        if sp.post_norms:
+            main["post2"] = get("norm2b", (H,))
+    side = None
+    if sp.type == "delta":
+        qk = sp.n_kv * sp.dim
+        main.update(q=get("mix.q", (qk, H)), k=get("mix.k", (qk, H)), v=get("mix.v", (sp.inner, H)), g=get("mix.g", (sp.inner, H)),
+                    o=get("mix.o", (H, sp.inner)), q_conv=get("mix.q.conv", (qk, sp.conv)), k_conv=get("mix.k.conv", (qk, sp.conv)),
+                    v_conv=get("mix.v.conv", (sp.inner, sp.conv)), beta=get("mix.b", (sp.heads, H)), a_proj=get("mix.a", (sp.heads, H)),
+                    a_log=get("mix.A_log", (sp.heads,)), dt_bias=get("mix.dt_bias", (sp.heads,)), norm=get("mix.norm", (sp.vdim,)))
+    else:
+        r = sp.side
+        sq, skv, svv = sp.heads * sp.dim, sp.n_kv * sp.dim, sp.n_kv * sp.vdim
+        rel = vb.get(f"{name}.mix.left.rel")
+        if rel is None or rel.dim() != 2 or rel.shape[1] != sp.heads:
+            raise ValueError(f"{name}.mix.left.rel must be [rows, {sp.heads}]")
+        sp.bias_rows = int(rel.shape[0])
+        main.update(q=get("mix.left.q", (sq, H)), q_b=get("mix.left.q.b", (sq,)), k=get("mix.left.k", (skv, H)), k_b=get("mix.left.k.b", (skv,)),
+                    v=get("mix.left.v", (svv, H)), v_b=get("mix.left.v.b", (svv,)), rel=rel, talk=get("mix.left.talk", (sp.heads, sp.heads)),
+                    g=get("mix.left.g", (sp.inner, H)), o=get("mix.left.o", (H, sp.inner)), o_b=get("mix.left.o.b", (H,)),
+                    branch_norm=get("mix.left.out", (H,)))
+        rq = r.heads * r.dim
+        side = dict(q=get("mix.right.q", (rq, H)), k=get("mix.right.k", (rq, H)), v=get("mix.right.v", (r.inner, H)), g=get("mix.right.g", (r.inner, H)),
+                    o=get("mix.right.o", (H, r.inner)), norm=get("mix.right.norm", (r.inner,)), i_proj=get("mix.right.i", (r.heads, H)),
+                    i_b=get("mix.right.i.b", (r.heads,)), f_proj=get("mix.right.f", (r.heads, H)), f_b=get("mix.right.f.b", (r.heads,)),
+                    branch_norm=get("mix.right.out", (H,)))
+    return main, side
+
+
 def detect_model_prefix(index_path: str, configured: str) -> str:
     """cake/mod.rs:335-357: the text before the first ``.layers.0.`` key of the index wins over the configured prefix."""
     if not os.path.exists(index_path):

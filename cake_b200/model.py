@@ -288,40 +288,75 @@ class MixerBlock(B200Transformer):
 
     @classmethod
     def load(cls, name: str, ctx: Context) -> "MixerBlock":
-        from .capi import CMixerSpec, CMixerTensors, CMoeSpec, CRotarySpec, MIXER_TENSOR_FIELDS
-        from .config import MIXER_KINDS
         from .loader import mixer_block_tensors
         cfg = ctx.config
         index = [cfg.layer_name(i) for i in range(len(cfg.layers))].index(name)
         sp = cfg.layers[index]
         views = mixer_block_tensors(ctx.var_builder, cfg, index)
-        keep, args = [], {}
-        for fld in MIXER_TENSOR_FIELDS:
-            t = views.get(fld)
-            if isinstance(t, list):
-                ts = [x.to(ctx.torch_dtype).contiguous() for x in t]
-                keep.append(ts)
-                args[fld] = ptr_array([ptr(x) for x in ts]) if ts else None
-            elif fld.startswith("e_"):
-                args[fld] = None
-            else:
-                t = None if t is None else t.to(ctx.torch_dtype).contiguous()
-                keep.append(t)
-                args[fld] = ptr(t)
-        r, mo = sp.rot, sp.moe
-        decay = (ctypes.c_float * max(1, len(sp.decay)))(*sp.decay)
-        spec = CMixerSpec(MIXER_KINDS[sp.type], sp.heads, sp.dim, sp.vdim, sp.rot_dim, sp.kv_rank, sp.scale,
-                          CRotarySpec(r.dims, r.base, r.factor, r.fast, r.slow, r.original),
-                          decay if sp.decay else None, sp.state, sp.groups, sp.conv, sp.norm_groups,
-                          CMoeSpec(mo.experts, mo.identity, mo.top, mo.scale, mo.ff, mo.shared_ff, mo.act) if mo else CMoeSpec())
-        tens = CMixerTensors(**args)
+        keep = []
+        spec, tens = _mixer_struct(sp, views, ctx, keep)
+        h = c_void_p()
+        check(lib().cake_b200_block_load_mixer(ctx.h, index, byref(spec), byref(tens), byref(h)))
+        return cls(name, h, ctx)
+
+
+def _mixer_struct(sp, views, ctx, keep):
+    """(CMixerSpec, CMixerTensors) of one MixerSpec and its tensors (by field name; missing = NULL); device / host copies
+    that must outlive the load call are appended to ``keep``."""
+    from .capi import CMixerSpec, CMixerTensors, CMoeSpec, CRotarySpec, MIXER_TENSOR_FIELDS
+    from .config import MIXER_KINDS
+    args = {}
+    for fld in MIXER_TENSOR_FIELDS:
+        t = views.get(fld)
+        if isinstance(t, list):
+            ts = [x.to(ctx.torch_dtype).contiguous() for x in t]
+            keep.append(ts)
+            arr = ptr_array([ptr(x) for x in ts]) if ts else None
+            keep.append(arr)
+            args[fld] = arr
+        elif fld.startswith("e_"):
+            args[fld] = None
+        else:
+            t = None if t is None else t.to(ctx.torch_dtype).contiguous()
+            keep.append(t)
+            args[fld] = ptr(t)
+    r, mo = sp.rot, sp.moe
+    decay = (ctypes.c_float * max(1, len(sp.decay)))(*sp.decay)
+    keep.append(decay)
+    spec = CMixerSpec(MIXER_KINDS[sp.type], sp.heads, sp.dim, sp.vdim, sp.rot_dim, sp.kv_rank, sp.scale,
+                      CRotarySpec(r.dims, r.base, r.factor, r.fast, r.slow, r.original),
+                      decay if sp.decay else None, sp.state, sp.groups, sp.conv, sp.norm_groups,
+                      CMoeSpec(mo.experts, mo.identity, mo.top, mo.scale, mo.ff, mo.shared_ff, mo.act) if mo else CMoeSpec(),
+                      sp.kv_heads, sp.bias_rows, sp.bias_max, sp.gate_cap, sp.norm_offset, sp.canon_taps, sp.dense_ff, sp.dense_act,
+                      sp.dense_limit, None)
+    return spec, CMixerTensors(**args)
+
+
+class SandwichBlock(MixerBlock):
+    """A layer of a Nuvarax model: a mixer-list block (``cake_b200_block_load_mixer``) with the structure switches set — gains
+    stored as offsets from one, a norm behind every sublayer, a convolution in front of the mixer, a dense clamped
+    feed-forward — whose mixer is a gated delta rule or attention with mixed heads beside a matrix memory."""
+
+    @classmethod
+    def load(cls, name: str, ctx: Context) -> "SandwichBlock":
+        from .loader import nuvarax_block_tensors
+        cfg = ctx.config
+        index = [cfg.layer_name(i) for i in range(len(cfg.layers))].index(name)
+        sp = cfg.layers[index]
+        main, side = nuvarax_block_tensors(ctx.var_builder, cfg, index)
+        keep = []
+        spec, tens = _mixer_struct(sp, main, ctx, keep)
+        if side is not None:
+            sspec, stens = _mixer_struct(sp.side, side, ctx, keep)
+            keep += [sspec, stens]
+            spec.side, tens.side = ctypes.pointer(sspec), ctypes.pointer(stens)
         h = c_void_p()
         check(lib().cake_b200_block_load_mixer(ctx.h, index, byref(spec), byref(tens), byref(h)))
         return cls(name, h, ctx)
 
 
 # Config.block_kind -> the Forwarder that loads and runs its layers
-BLOCK_CLASSES = {"nigenex": ListedBlock, "setodra": MixerBlock}
+BLOCK_CLASSES = {"nigenex": ListedBlock, "setodra": MixerBlock, "nuvarax": SandwichBlock}
 
 
 @dataclass
@@ -368,6 +403,17 @@ class TextModelBase:
         lnf = rms_norm_weight(get(n_norm, () if cfg.scalar_final_norm else (cfg.hidden_size,)), cfg)   # text_model.rs:186-192
         head = None if n_head is None else get(n_head, (cfg.vocab_size, cfg.hidden_size))
         check(lib().cake_b200_head_load(ctx.h, ptr(emb), ptr(lnf), ptr(head)))
+        tables = cfg.pair_embedding or cfg.learned_positions or cfg.final_norm_offset
+        if tables:   # embeddings that depend on a token's place in its sequence; the final norm's gain offset
+            from .capi import CEmbedTables
+            pe = cfg.pair_embedding
+            big = get("bigram", (pe["buckets"] + 1, cfg.hidden_size)) if pe else None
+            pos = vb["pos"].to(ctx.torch_dtype).contiguous() if cfg.learned_positions else None
+            if pos is not None and (pos.dim() != 2 or pos.shape[1] != cfg.hidden_size):
+                raise ValueError(f"shape mismatch for pos, expected: [positions, {cfg.hidden_size}], got: {list(pos.shape)}")
+            et = CEmbedTables(ptr(big), pe["buckets"] + 1 if pe else 0, pe["mul_prev"] if pe else 0, pe["mul_cur"] if pe else 0,
+                              ptr(pos), int(pos.shape[0]) if pos is not None else 0, float(cfg.final_norm_offset))
+            check(lib().cake_b200_head_load_tables(ctx.h, byref(et)))
         blocks: List[Forwarder] = []
         loaded: Dict[int, Forwarder] = {}   # a layer of a looped range appears once per pass and is loaded once
         plan = cfg.run_plan() if cfg.layer_list else [(i, None) for i in range(cfg.num_hidden_layers)]
@@ -386,7 +432,8 @@ class TextModelBase:
             loaded[i] = blocks[-1]
         model = cls(ctx, blocks, **kw)
         # run index -> pass number, for the runs in front of which the stream receives the pass's additions
-        model.injections = {j: t for j, (_, t) in enumerate(plan) if t is not None}
+        model.injections = {j: t for j, (_, t) in enumerate(plan) if t is not None} if cfg.loop_injects else {}
+        model.embed_at = bool(cfg.pair_embedding or cfg.learned_positions)
         if model.injections:
             steps = get("loop.step", (int(cfg.loop["times"]), cfg.hidden_size))
             model.loop_steps = [steps[t].contiguous() for t in range(steps.shape[0])]
@@ -401,7 +448,10 @@ class TextModelBase:
         b, s = ids.shape
         ctx = self.ctx
         x = ctx.empty(b, s, ctx.config.hidden_size, dtype=ctx.stream_dtype)
-        check(lib().cake_b200_embed(ctx.h, ids.ctypes.data_as(ctypes.POINTER(c_uint32)), b, s, ptr(x)))
+        if getattr(self, "embed_at", False):   # the cache supplies the previous token of every row and checks the position
+            check(lib().cake_b200_embed_at(ctx.h, ctx.cache.h, ids.ctypes.data_as(ctypes.POINTER(c_uint32)), b, s, idx, ptr(x)))
+        else:
+            check(lib().cake_b200_embed(ctx.h, ids.ctypes.data_as(ctypes.POINTER(c_uint32)), b, s, ptr(x)))
         n, i = len(self.blocks), 0
         inject = getattr(self, "injections", None) or {}
         x0 = x if inject else None

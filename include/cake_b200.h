@@ -193,10 +193,41 @@ int cake_b200_block_load_spec(cake_b200_ctx *, int layer_idx, const cake_b200_la
  * The feed-forward (moe.experts + moe.identity > 0): router logits router h in fp32, s = softmax over all experts; the `top`
  * largest s + correction are chosen; their weights are s / (sum of the chosen s + 1e-20) * scale.  Experts [0, experts) are
  * down(act(gate h) * (up h)); the last `identity` router outputs return h itself.  shared_ff > 0: one more expert of that
- * width runs for every token, times sigmoid(s_sg . h). */
+ * width runs for every token, times sigmoid(s_sg . h).
+ *   CAKE_B200_MIX_DELTA      gated delta rule.  q, k ([kv_heads * dim, hidden]; head h reads q / k head h / (heads / kv_heads)) and
+ *                            v ([heads * vdim, hidden]) pass a causal convolution per channel (q_conv / k_conv / v_conv [channels, conv],
+ *                            last tap = the current token, no bias) + silu; q and k become unit vectors per head,
+ *                            x / sqrt(sum x^2 + 1e-6), q times dim^-1/2; beta = sigmoid(beta h), decay g = exp(-exp(a_log_h)
+ *                            softplus(a_proj h + dt_bias_h)) per head; S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q;
+ *                            o of every head divided by its root mean square, times norm [vdim], times silu(g h), then o.
+ *   CAKE_B200_MIX_TALKING_ATTENTION  grouped-query softmax attention without rotation, causal over every cached key; q / k / v / o
+ *                            with biases (q_b, k_b, v_b, o_b); score = (q . k) * scale + rel[bucket(i - j), head], where with
+ *                            R = bias_rows, h = R / 2: bucket(n) = n for n < h, else min(R - 1, h + floor(ln(n / h) /
+ *                            ln(bias_max / h) * (R - h))); after the softmax the heads' weights are mixed, w_h <- sum_g
+ *                            talk[h, g] w_g, and head h applies its mixed weights to the values of its own kv head; the
+ *                            concatenated heads are multiplied by sigmoid(g h); then o.
+ *   CAKE_B200_MIX_MATRIX_MEMORY  a matrix memory with exponential gates.  q (times dim^-1/2), k [heads * dim, hidden], v
+ *                            [heads * vdim, hidden]; log gates per head i = cap tanh((i_proj h + i_b) / cap), f = logsigmoid(cap
+ *                            tanh((f_proj h + f_b) / cap)), cap = gate_cap; running maximum m (0 at the start): m' = max(f + m, i);
+ *                            S <- exp(f + m - m') S + exp(i - m') k v^T, n likewise with k alone; o = S^T q / (max(|n . q|,
+ *                            exp(-m')) + 1e-6); o of every head divided by its root mean square, times norm [heads * vdim], times
+ *                            sigmoid(g h), then o.  S, n and m live in the cache in fp32.
+ * Block structure switches (all 0 / NULL for the plain pre-norm block above):
+ *   norm_offset  the gains of norm1 / norm2 / post1 / post2 are stored as offsets: gain = stored + norm_offset (computed in fp32)
+ *   post1, post2 an RMS norm of the mixer's / feed-forward's output before it is added to the stream
+ *   canon_taps   > 1: the mixer reads h + conv(h), a causal convolution over time per channel of the normed input (canon
+ *                [hidden, canon_taps], last tap = the current token, no bias, fp32); its last canon_taps - 1 inputs live in the cache
+ *   side         a second mixer that reads the same input: both outputs are RMS-normed over the width with plain gains
+ *                (branch_norm of each mixer's tensors) and averaged; the side mixer's spec / tensors use the mixer fields only
+ *   dense_ff     > 0: a dense gated feed-forward of that width instead of the routed one (ff_gate, ff_up [dense_ff, hidden],
+ *                ff_down [hidden, dense_ff]); dense_act 0 silu(g) u, 1 tanh-gelu(g) u, 2: g' = min(g, dense_limit), u' = clamp(u,
+ *                -dense_limit, dense_limit), g' sigmoid(1.702 g') (u' + 1) */
 #define CAKE_B200_MIX_LATENT 1
 #define CAKE_B200_MIX_RETENTION 2
 #define CAKE_B200_MIX_STATE_SPACE 3
+#define CAKE_B200_MIX_DELTA 4
+#define CAKE_B200_MIX_TALKING_ATTENTION 5
+#define CAKE_B200_MIX_MATRIX_MEMORY 6
 typedef struct cake_b200_rotary_spec {
   int dims;            /* 0 = no rotation */
   double base;
@@ -217,8 +248,17 @@ typedef struct cake_b200_mixer_spec {
   float scale;            /* latent */
   cake_b200_rotary_spec rot;
   const float *decay;     /* retention: [heads], host */
-  int state, groups, conv, norm_groups;  /* state space; dim is ignored (state is the key size) */
+  int state, groups, conv, norm_groups;  /* state space; dim is ignored (state is the key size); conv also: delta */
   cake_b200_moe_spec moe;
+  int kv_heads;           /* delta, talking attention (0 = heads) */
+  int bias_rows;          /* talking attention: rows of rel (0 = no distance bias) */
+  float bias_max;
+  float gate_cap;         /* matrix memory */
+  float norm_offset;
+  int canon_taps;
+  int dense_ff, dense_act;
+  float dense_limit;
+  const struct cake_b200_mixer_spec *side;
 } cake_b200_mixer_spec;
 typedef struct cake_b200_mixer_tensors {
   const void *norm1, *norm2;                 /* [hidden]; norm2 NULL without a feed-forward */
@@ -228,6 +268,13 @@ typedef struct cake_b200_mixer_tensors {
   const void *router, *correction;           /* [experts+identity, hidden], [experts+identity] */
   const void *const *e_gate, *const *e_up, *const *e_down;  /* `experts` pointers each: [ff, hidden] x2, [hidden, ff] */
   const void *s_gate, *s_up, *s_down, *s_sg; /* shared expert; s_sg [hidden] */
+  const void *post1, *post2, *canon;         /* [hidden], [hidden], [hidden, canon_taps] */
+  const void *q_conv, *k_conv, *v_conv, *beta, *a_proj;  /* delta: [kv_heads*dim, conv] x2, [heads*vdim, conv], [heads, hidden] x2 */
+  const void *q_b, *k_b, *v_b, *o_b, *rel, *talk;        /* talking attention: biases, [bias_rows, heads], [heads, heads] */
+  const void *i_proj, *i_b, *f_proj, *f_b;   /* matrix memory: [heads, hidden], [heads] each */
+  const void *ff_gate, *ff_up, *ff_down;     /* dense feed-forward */
+  const void *branch_norm;                   /* [hidden]: with a side mixer, the gain of this mixer's output norm */
+  const struct cake_b200_mixer_tensors *side;
 } cake_b200_mixer_tensors;
 int cake_b200_block_load_mixer(cake_b200_ctx *, int layer_idx, const cake_b200_mixer_spec *, const cake_b200_mixer_tensors *,
                                cake_b200_block **out);
@@ -262,6 +309,21 @@ int cake_b200_forward_batch_host(cake_b200_ctx *, cake_b200_block *const *blocks
 /* ---- head / tail (master role) ---------------------------------------------------------------- */
 int cake_b200_head_load(cake_b200_ctx *, const void *embed, const void *ln_f, const void *lm_head /* NULL if tied */);
 int cake_b200_embed(cake_b200_ctx *, const uint32_t *ids_host, int batch, int seq, void *x_dev);
+/* Embeddings that depend on the place of a token in its sequence (layer-list models, fp32 stream), added to the scaled token
+ * embedding:  a hashed pair embedding, row (previous token * mul_prev + token * mul_cur) mod (bigram_rows - 1) of bigram
+ * [bigram_rows, hidden], the last row for a sequence's first token;  and a learned vector per position, pos [pos_rows, hidden].
+ * Either pointer may be NULL.  final_norm_offset: the final norm's gain is stored as an offset from this number.  Call after
+ * cake_b200_head_load.  With tables loaded, the stream starts with cake_b200_embed_at: the cache supplies the previous token
+ * of every batch row and checks index_pos against the position the embedding has reached in it. */
+typedef struct cake_b200_embed_tables {
+  const void *bigram;
+  int bigram_rows, mul_prev, mul_cur;
+  const void *pos;
+  int pos_rows;
+  float final_norm_offset;
+} cake_b200_embed_tables;
+int cake_b200_head_load_tables(cake_b200_ctx *, const cake_b200_embed_tables *);
+int cake_b200_embed_at(cake_b200_ctx *, cake_b200_cache *, const uint32_t *ids_host, int batch, int seq, int index_pos, void *x_dev);
 /* ln_f on the last position of each batch row, lm_head, logits (batch, vocab) in D written to
  * logits_dev (nullable); if argmax_host != NULL also computes the greedy token per row
  * (first maximum wins), copies it to argmax_host and synchronises. */

@@ -108,6 +108,21 @@ extern "C" {
         tensors: *const cake_b200_mixer_tensors, out: *mut *mut cake_b200_block) -> c_int;
     pub fn cake_b200_stream_inject(ctx: *mut cake_b200_ctx, x_dev: *mut f32, x0_dev: *const f32, vec: *const c_void, slot: c_int,
         rows: c_int) -> c_int;
+    pub fn cake_b200_head_load_tables(ctx: *mut cake_b200_ctx, tables: *const cake_b200_embed_tables) -> c_int;
+    pub fn cake_b200_embed_at(ctx: *mut cake_b200_ctx, cache: *mut cake_b200_cache, ids_host: *const u32, batch: c_int, seq: c_int,
+        index_pos: c_int, x_dev: *mut c_void) -> c_int;
+}
+
+/// `cake_b200_embed_tables` (include/cake_b200.h): a hashed pair embedding, learned position vectors, the final norm's gain offset.
+#[repr(C)]
+pub struct cake_b200_embed_tables {
+    pub bigram: *const c_void,
+    pub bigram_rows: c_int,
+    pub mul_prev: c_int,
+    pub mul_cur: c_int,
+    pub pos: *const c_void,
+    pub pos_rows: c_int,
+    pub final_norm_offset: f32,
 }
 
 /// `cake_b200_rotary_spec`, `cake_b200_moe_spec`, `cake_b200_mixer_spec`, `cake_b200_mixer_tensors` (include/cake_b200.h): a
@@ -147,6 +162,17 @@ pub struct cake_b200_mixer_spec {
     pub conv: c_int,
     pub norm_groups: c_int,
     pub moe: cake_b200_moe_spec,
+    // delta / talking-attention / matrix-memory mixers and the block structure switches
+    pub kv_heads: c_int,
+    pub bias_rows: c_int,
+    pub bias_max: f32,
+    pub gate_cap: f32,
+    pub norm_offset: f32,
+    pub canon_taps: c_int,
+    pub dense_ff: c_int,
+    pub dense_act: c_int,
+    pub dense_limit: f32,
+    pub side: *const cake_b200_mixer_spec,
 }
 #[repr(C)]
 pub struct cake_b200_mixer_tensors {
@@ -177,6 +203,29 @@ pub struct cake_b200_mixer_tensors {
     pub s_up: *const c_void,
     pub s_down: *const c_void,
     pub s_sg: *const c_void,
+    pub post1: *const c_void,
+    pub post2: *const c_void,
+    pub canon: *const c_void,
+    pub q_conv: *const c_void,
+    pub k_conv: *const c_void,
+    pub v_conv: *const c_void,
+    pub beta: *const c_void,
+    pub a_proj: *const c_void,
+    pub q_b: *const c_void,
+    pub k_b: *const c_void,
+    pub v_b: *const c_void,
+    pub o_b: *const c_void,
+    pub rel: *const c_void,
+    pub talk: *const c_void,
+    pub i_proj: *const c_void,
+    pub i_b: *const c_void,
+    pub f_proj: *const c_void,
+    pub f_b: *const c_void,
+    pub ff_gate: *const c_void,
+    pub ff_up: *const c_void,
+    pub ff_down: *const c_void,
+    pub branch_norm: *const c_void,
+    pub side: *const cake_b200_mixer_tensors,
 }
 
 /// `cake_b200_block_variant` (include/cake_b200.h): norm placement and per-layer attention mode of the OLMo2 / Gemma3 /
