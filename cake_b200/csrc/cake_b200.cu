@@ -1658,7 +1658,7 @@ extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const
                                           cake_b200_block **out) {
   if (!c || !sp || !t || !out) return fail(CAKE_B200_EINVAL, "null argument");
   if (!c->cfg.layer_list) return fail(CAKE_B200_EINVAL, "block_load_mixer needs a ctx created with layer_list = 1");
-  if (mixer_kind_ext(sp->kind) || sp->side || sp->norm_offset != 0.f || sp->canon_taps > 1 || sp->dense_ff > 0 || t->post1 || t->post2)
+  if (mixer_kind_ext(sp->kind) || sp->side || sp->norm_offset != 0.f || sp->canon_taps > 0 || sp->dense_ff > 0 || t->post1 || t->post2)
     return load_mixer_ext(c, layer_idx, sp, t, out);
   const cake_b200_moe_spec &mo = sp->moe;
   const bool has_ff = mo.experts + mo.identity > 0;
@@ -1908,7 +1908,7 @@ static int load_mixer_ext(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer
   if (!t->norm1) return fail(CAKE_B200_EINVAL, "layer %d: null norm1", layer_idx);
   if (sp->moe.experts + sp->moe.identity > 0) return fail(CAKE_B200_EINVAL, "layer %d: the routed feed-forward is not built for this block structure", layer_idx);
   if (sp->side && (!t->side || !t->branch_norm || !t->side->branch_norm)) return fail(CAKE_B200_EINVAL, "layer %d: a side mixer needs its tensors and both branch norms", layer_idx);
-  if (sp->canon_taps < 0 || (sp->canon_taps > 1 && !t->canon)) return fail(CAKE_B200_EINVAL, "layer %d: canon_taps %d without canon", layer_idx, sp->canon_taps);
+  if (sp->canon_taps < 0 || (sp->canon_taps > 0 && !t->canon)) return fail(CAKE_B200_EINVAL, "layer %d: canon_taps %d without canon", layer_idx, sp->canon_taps);
   if (sp->dense_ff < 0 || (sp->dense_ff > 0 && (!t->ff_gate || !t->ff_up || !t->ff_down || !t->norm2 || sp->dense_act < 0 || sp->dense_act > 2)))
     return fail(CAKE_B200_EINVAL, "layer %d: a dense feed-forward needs norm2 / ff_gate / ff_up / ff_down and dense_act in 0..2", layer_idx);
   CU(cudaSetDevice(c->device));
@@ -1951,7 +1951,7 @@ static int load_mixer_ext(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer
     }
     RC(upload(c, &b->ln1, t->norm1, H * es));
     if (t->post1) RC(upload(c, &b->post1, t->post1, H * es));
-    if (sp->canon_taps > 1) RC(upload(c, &b->canon, t->canon, H * sp->canon_taps * es));
+    if (sp->canon_taps > 0) RC(upload(c, &b->canon, t->canon, H * sp->canon_taps * es));
     if (sp->dense_ff > 0) {  // row-interleaved gate / up as everywhere else
       const size_t I = sp->dense_ff;
       RC(upload(c, &b->ln2, t->norm2, H * es));
@@ -2051,7 +2051,7 @@ static ExtScratch ext_scratch(const cake_b200_ctx *c, const cake_b200_block *b, 
   };
   const size_t es = c->es, H = c->cfg.hidden;
   s.h = take(M * H * es);
-  if (b->ms.canon_taps > 1) s.h32 = (float *)take(M * H * sizeof(float));
+  if (b->ms.canon_taps > 0) s.h32 = (float *)take(M * H * sizeof(float));
   s.proj = take(M * b->n_in_pad * es);
   s.a = sub_scratch(c, b, M, n_keys, take);
   if (b->side) s.b = sub_scratch(c, b->side, M, n_keys, take);
@@ -2120,9 +2120,9 @@ static int enqueue_ext_layer(cake_b200_ctx *c, const cake_b200_block *b, int l, 
   cudaStream_t st = c->stream;
   const ExtScratch w = ext_scratch(c, b, (size_t)M, (char *)c->mx_ws, pos0 + S);
   // 1. h = norm1(x), the input convolution, every projection of the mixer(s) in one product
-  mx::RmsRows n1{cur, b->ln1, sp.norm_offset, sp.canon_taps > 1 ? w.h32 : nullptr, sp.canon_taps > 1 ? nullptr : w.h, M, H, eps};
+  mx::RmsRows n1{cur, b->ln1, sp.norm_offset, sp.canon_taps > 0 ? w.h32 : nullptr, sp.canon_taps > 0 ? nullptr : w.h, M, H, eps};
   MX(mx::rms_rows(st, dt, n1, lc));
-  if (sp.canon_taps > 1) {
+  if (sp.canon_taps > 0) {
     mx::CanonConv cc{w.h32, b->canon, kc->canon_hist[l], w.h, B, S, H, sp.canon_taps, pos0};
     MX(mx::canon_conv(st, dt, cc, lc));
   }

@@ -364,7 +364,7 @@ def nuvarax_block_tensors(vb, cfg: Config, index: int):
     main = {"norm1": get("norm1", (H,))}
     if sp.post_norms:
         main["post1"] = get("norm1b", (H,))
-    if sp.canon_taps > 1:
+    if sp.canon_taps >= 1:
         main["canon"] = get("canon1", (H, sp.canon_taps))
     if sp.dense_ff:
         main.update(norm2=get("norm2", (H,)), ff_gate=get("mlp.gate", (sp.dense_ff, H)), ff_up=get("mlp.up", (sp.dense_ff, H)),

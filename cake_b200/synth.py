@@ -224,3 +224,60 @@ def make_mixer_checkpoint(cfg: Config, dtype: str = "bf16", seed: int = 1234, de
                 sd[f"{p}.mlp.shared.gate"], sd[f"{p}.mlp.shared.up"] = rn(mo.shared_ff, H, s=2 * std), rn(mo.shared_ff, H, s=2 * std)
                 sd[f"{p}.mlp.shared.down"], sd[f"{p}.mlp.shared.sg"] = rn(H, mo.shared_ff, s=2 * std), rn(1, H, s=4 * std)
     return sd
+
+
+def make_nuvarax_checkpoint(cfg: Config, dtype: str = "bf16", seed: int = 1234, device="cpu", std: float = 0.05) -> dict:
+    """Random weights of a Nuvarax model under the names its checkpoints use: ``embed`` (also the output projection), ``bigram``
+    [buckets + 1, width], ``pos`` [positions, width], ``final.norm`` and per layer ``l<i>.{norm1, norm1b, norm2, norm2b}`` (gains
+    stored as offsets from one), ``l<i>.canon1`` [width, taps], ``l<i>.mlp.{gate, up, down}`` and the mixer under ``l<i>.mix.``:
+    a delta layer has ``q, k, v`` (each with ``.conv``), ``b``, ``a``, ``A_log``, ``dt_bias``, ``norm`` [vdim], ``g``, ``o``; a parallel
+    layer ``left.{q, k, v, o}`` (each with ``.b``), ``left.{rel, talk, g, out}`` and ``right.{q, k, v, g, o, norm, out}``,
+    ``right.{i, f}`` (each with ``.b``).  ``rel`` has ``bias_rows`` rows (32 when the spec leaves it 0)."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed * 1000003 + 909091)
+    td, H = TORCH_DTYPES[dtype], cfg.hidden_size
+
+    def rn(*shape, s=std):
+        return (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * s).to(td)
+
+    def ru(*shape, lo=0.0, hi=1.0):
+        return (torch.rand(shape, generator=gen, device=device, dtype=torch.float32) * (hi - lo) + lo).to(td)
+
+    sd = {"embed": rn(cfg.vocab_size, H, s=0.3), "final.norm": rn(H, s=0.1)}
+    if cfg.pair_embedding:
+        sd["bigram"] = rn(cfg.pair_embedding["buckets"] + 1, H, s=0.5)
+    if cfg.learned_positions:
+        sd["pos"] = rn(cfg.learned_positions, H, s=0.5)
+    for i, sp in enumerate(cfg.layers):
+        p = cfg.layer_name(i)
+        sd[f"{p}.norm1"] = rn(H, s=0.1)
+        if sp.post_norms:
+            sd[f"{p}.norm1b"] = rn(H, s=0.1)
+        if sp.canon_taps >= 1:
+            sd[f"{p}.canon1"] = rn(H, sp.canon_taps, s=0.3)
+        if sp.dense_ff:
+            sd[f"{p}.norm2"] = rn(H, s=0.1)
+            if sp.post_norms:
+                sd[f"{p}.norm2b"] = rn(H, s=0.1)
+            sd[f"{p}.mlp.gate"], sd[f"{p}.mlp.up"], sd[f"{p}.mlp.down"] = rn(sp.dense_ff, H, s=4 * std), rn(sp.dense_ff, H, s=4 * std), rn(H, sp.dense_ff)
+        if sp.type == "delta":
+            qk, m = sp.n_kv * sp.dim, f"{p}.mix"
+            sd[f"{m}.q"], sd[f"{m}.k"], sd[f"{m}.v"] = rn(qk, H, s=2 * std), rn(qk, H, s=2 * std), rn(sp.inner, H, s=2 * std)
+            sd[f"{m}.q.conv"], sd[f"{m}.k.conv"], sd[f"{m}.v.conv"] = rn(qk, sp.conv, s=0.4), rn(qk, sp.conv, s=0.4), rn(sp.inner, sp.conv, s=0.4)
+            sd[f"{m}.b"], sd[f"{m}.a"] = rn(sp.heads, H, s=2 * std), rn(sp.heads, H, s=2 * std)
+            sd[f"{m}.A_log"], sd[f"{m}.dt_bias"] = ru(sp.heads, lo=-2.5, hi=0.5), ru(sp.heads, lo=-3.0, hi=0.5)
+            sd[f"{m}.norm"], sd[f"{m}.g"], sd[f"{m}.o"] = ru(sp.vdim, lo=0.8, hi=1.2), rn(sp.inner, H, s=2 * std), rn(H, sp.inner)
+        else:
+            a, r, rows = f"{p}.mix.left", sp.side, sp.bias_rows or 32
+            sq, skv, svv = sp.heads * sp.dim, sp.n_kv * sp.dim, sp.n_kv * sp.vdim
+            sd[f"{a}.q"], sd[f"{a}.k"], sd[f"{a}.v"] = rn(sq, H, s=4 * std), rn(skv, H, s=4 * std), rn(svv, H, s=2 * std)
+            sd[f"{a}.q.b"], sd[f"{a}.k.b"], sd[f"{a}.v.b"], sd[f"{a}.o.b"] = rn(sq, s=0.2), rn(skv, s=0.2), rn(svv, s=0.2), rn(H, s=0.2)
+            sd[f"{a}.rel"] = rn(rows, sp.heads, s=0.7)
+            sd[f"{a}.talk"] = (torch.eye(sp.heads, device=device) * 0.7 + torch.randn((sp.heads, sp.heads), generator=gen, device=device) * 0.25).to(td)
+            sd[f"{a}.g"], sd[f"{a}.o"], sd[f"{a}.out"] = rn(sp.inner, H, s=2 * std), rn(H, sp.inner), ru(H, lo=0.8, hi=1.2)
+            b, rq = f"{p}.mix.right", r.heads * r.dim
+            sd[f"{b}.q"], sd[f"{b}.k"], sd[f"{b}.v"], sd[f"{b}.g"] = rn(rq, H, s=2 * std), rn(rq, H, s=2 * std), rn(r.inner, H, s=2 * std), rn(r.inner, H, s=2 * std)
+            sd[f"{b}.o"], sd[f"{b}.norm"], sd[f"{b}.out"] = rn(H, r.inner), ru(r.inner, lo=0.8, hi=1.2), ru(H, lo=0.8, hi=1.2)
+            sd[f"{b}.i"], sd[f"{b}.f"] = rn(r.heads, H, s=4 * std), rn(r.heads, H, s=4 * std)
+            sd[f"{b}.i.b"], sd[f"{b}.f.b"] = rn(r.heads, s=0.5), ru(r.heads, lo=1.0, hi=4.0)
+    return sd

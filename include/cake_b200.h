@@ -215,7 +215,7 @@ int cake_b200_block_load_spec(cake_b200_ctx *, int layer_idx, const cake_b200_la
  * Block structure switches (all 0 / NULL for the plain pre-norm block above):
  *   norm_offset  the gains of norm1 / norm2 / post1 / post2 are stored as offsets: gain = stored + norm_offset (computed in fp32)
  *   post1, post2 an RMS norm of the mixer's / feed-forward's output before it is added to the stream
- *   canon_taps   > 1: the mixer reads h + conv(h), a causal convolution over time per channel of the normed input (canon
+ *   canon_taps   >= 1: the mixer reads h + conv(h), a causal convolution over time per channel of the normed input (canon
  *                [hidden, canon_taps], last tap = the current token, no bias, fp32); its last canon_taps - 1 inputs live in the cache
  *   side         a second mixer that reads the same input: both outputs are RMS-normed over the width with plain gains
  *                (branch_norm of each mixer's tensors) and averaged; the side mixer's spec / tensors use the mixer fields only

@@ -49,7 +49,7 @@ def embed(tokens, wt, cfg, dt):
         rows = (prev * int(bg["mul_prev"]) + ids * int(bg["mul_cur"])) % nb
         rows[0] = nb          # the first token of a sequence has no predecessor: the table's last row
         x = x + wt["bigram"].to(dt)[rows]
-    return x + wt["pos"].to(dt)[: len(tokens)]
+    return x + wt["pos"].to(dt)[: len(tokens)] if "pos" in wt else x
 
 
 def distance_bucket(n, rows, dmax):
@@ -58,6 +58,9 @@ def distance_bucket(n, rows, dmax):
     if n < half:
         return n
     return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(dmax / half) * (rows - half))))
+
+
+KEYS_VISIBLE = None   # tests only: an int hides keys further back than that, to show that far keys matter in a test's model
 
 
 def mixed_attention(h, wt, p, m):
@@ -74,6 +77,8 @@ def mixed_attention(h, wt, p, m):
     kk, vv = k.repeat_interleave(H // G, 1), v.repeat_interleave(H // G, 1)
     s = torch.einsum("ihd,jhd->hij", q, kk) * float(m["scale"]) + rel[idx].permute(2, 0, 1)
     vis = torch.arange(S)[:, None] >= torch.arange(S)[None, :]
+    if KEYS_VISIBLE is not None:
+        vis = vis & (torch.arange(S)[:, None] - torch.arange(S)[None, :] < KEYS_VISIBLE)
     pr = torch.softmax(s.masked_fill(~vis[None], float("-inf")), -1)
     pr = torch.einsum("hg,gij->hij", wt[p + "talk"].to(h.dtype), pr)
     o = torch.einsum("hij,jhv->ihv", pr, vv).reshape(S, H * V)
@@ -164,7 +169,8 @@ def forward(tokens, wt, cfg, dt=torch.float32, streams=None):
     for i in run_order(cfg):
         L, p = cfg["layers"][i], f"l{i}."
         h = norm1p(x, wt[p + "norm1"], eps)
-        h = h + causal_conv(h, wt[p + "canon1"])
+        if (cfg.get("canon") or {}).get("taps"):
+            h = h + causal_conv(h, wt[p + "canon1"])
         if L["type"] == "delta":
             y = delta_mixer(h, wt, p + "mix.", L["mixer"], eps)
         elif L["type"] == "parallel":
