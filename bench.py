@@ -9,6 +9,7 @@ Llama-3-8B bf16, bs=1, 2k context, layers sharded over N GPUs of one box (N=1 ->
     python bench.py --workload prefill                            # BASELINE configs[4] as the main line
     python bench.py --workload nigenex [--sizes 2k,4k,4k-hd64]    # the Nigenex design beside the closest existing block
     python bench.py --workload setodra [--sizes 1k,2k]            # the Setodra design beside the closest existing model
+    python bench.py --workload nuvarax [--sizes 1k,2k]            # the Nuvarax design beside the closest existing model
 
 A "step" is one decoded token: one pass of the hot path (embed -> blocks -> ln_f/lm_head/argmax) at batch 1.
 tok/s follows the reference's definition (master.rs:131-166): prefill excluded.  Prints ONE JSON line (rank 0).
@@ -1137,6 +1138,145 @@ def setodra_leg(env: Env, sizes=("1k", "2k"), batch: int = 4, seq: int = 4096, c
             "peaks": {"tensor_tflops": pk["tc"], "hbm_gbs": pk["hbm"], "source": pk["src"]}, "sizes": out}
 
 
+NUVARAX_SIZES = {  # layer sizes of real models (random weights): [attention beside a matrix memory, delta rule] x 2, each with a dense feed-forward
+    "1k": dict(width=1024, ff=4224, left=dict(heads=8, kv_heads=2, dim=128, vdim=128), right=dict(heads=4, dim=128, vdim=128),
+               delta=dict(heads=8, kv_heads=8, dim=128, vdim=128, conv=4)),
+    "2k": dict(width=2048, ff=11264, left=dict(heads=16, kv_heads=4, dim=128, vdim=128), right=dict(heads=8, dim=128, vdim=128),
+               delta=dict(heads=16, kv_heads=16, dim=128, vdim=128, conv=4)),
+}
+
+
+def _time_listed_model(env: Env, cfg, sd, batch: int, seq: int, ctx_len: int, steps: int, reps: int, mseq: int) -> dict:
+    """Prefill (one step of batch x seq tokens from an empty cache + the head on the last positions) and bs=1 decode (a
+    ctx_len-token prompt, then `steps` single-token steps) of a layer-list model through TextModelBase; device time by CUDA events."""
+    import torch
+    from cake_b200.model import Cache, Context, TextModelBase
+    vocab = cfg.vocab_size
+    ctx = Context(cfg, sd, "bf16", device=env.local, max_seq=mseq)
+    model = TextModelBase.load(ctx)
+    torch.cuda.empty_cache()
+    ctx.cache = Cache(ctx, batch, seq)
+    ids = torch.randint(0, vocab, (batch, seq), generator=torch.Generator().manual_seed(11)).numpy()
+    times, launches = [], 0
+    for rr in range(reps + 1):
+        ctx.cache.clear()
+        ctx.sync()
+        l0 = ctx.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ctx.torch_stream)
+        logits = model.forward(ids, 0)
+        e1.record(ctx.torch_stream)
+        ctx.sync()
+        if rr > 0:
+            times.append(e0.elapsed_time(e1))
+            launches += ctx.launch_count() - l0
+    pre = {"ms": statistics.median(times), "finite": bool(torch.isfinite(logits.float()).all()), "launches": (ctx.launch_count() - l0)}
+    ctx.cache = Cache(ctx, 1, mseq)
+    ids1 = torch.randint(0, vocab, (ctx_len + steps + 3,), generator=torch.Generator().manual_seed(3)).tolist()
+    model.forward([ids1[:ctx_len]], 0)
+    pos = ctx_len
+    for _ in range(3):
+        model.forward([[ids1[pos]]], pos)
+        pos += 1
+    ctx.sync()
+    l0 = ctx.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(ctx.torch_stream)
+    for _ in range(steps):
+        lg = model.forward([[ids1[pos]]], pos)
+        pos += 1
+    e1.record(ctx.torch_stream)
+    ctx.sync()
+    launches += ctx.launch_count() - l0
+    dec = {"ms_per_token": e0.elapsed_time(e1) / steps, "launches_per_token": (ctx.launch_count() - l0) / steps, "finite": bool(torch.isfinite(lg.float()).all())}
+    ctx.close()
+    del model, ctx
+    torch.cuda.empty_cache()
+    return {"prefill": pre, "decode": dec, "launches": launches}
+
+
+def nuvarax_leg(env: Env, sizes=("1k", "2k"), batch: int = 4, seq: int = 4096, ctx_len: int = 2048, steps: int = 32, reps: int = 3) -> dict:
+    """`--workload nuvarax`: the Nuvarax design (mixer-list blocks with norms on both sides of every sublayer and an input
+    convolution: attention with mixed heads beside a matrix memory, delta rule, attention + memory, delta rule, each followed by a
+    dense clamped feed-forward) beside the framework's closest existing model, Setodra (the other mixer-list model: latent
+    attention, retention, latent attention, retention, each with a routed feed-forward of the same active width), at equal width
+    and layer count, both through TextModelBase / forward_batch.  Workload and timing as in the Setodra leg."""
+    import torch
+    from cake_b200.config import Config, MixerSpec, MoeSpec, RotarySpec
+    from cake_b200.synth import make_mixer_checkpoint, make_nuvarax_checkpoint
+    pk = peaks()
+    out, launches, vocab = {}, 0, 32768
+    mseq = max(seq, ctx_len + steps + 8)
+    for name in sizes:
+        z, zs = NUVARAX_SIZES[name], SETODRA_SIZES[name]
+        W, ff = z["width"], z["ff"]
+        row = {"size": z}
+        for arch in ("nuvarax", "closest"):
+            if arch == "nuvarax":
+                a, b, dl = z["left"], z["right"], z["delta"]
+                layer = lambda kind, m: {"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}}
+                par = {"left": dict(scale=a["dim"] ** -0.5, bias_max=1024, **a), "right": dict(gate_cap=15.0, **b)}
+                d = {"architecture": "Nuvarax", "width": W, "vocab": vocab, "norm": {"eps": 1e-6}, "max_positions": mseq, "canon": {"taps": 4},
+                     "embedding": {"scale": 1.0, "bigram": {"buckets": 99991, "mul_prev": 1009, "mul_cur": 31}},
+                     "layers": [layer("parallel", par), layer("delta", dl), layer("parallel", par), layer("delta", dl)]}
+                cfg = Config.from_hf(d)
+                cfg.max_seq_len = mseq
+                sd = make_nuvarax_checkpoint(cfg, "bf16", seed=5, device=env.dev, std=0.02)
+                Ha, Ga, Hb, Hd = a["heads"], a["kv_heads"], b["heads"], dl["heads"]
+                n_par = Ha * a["dim"] + Ga * (a["dim"] + a["vdim"]) + Ha * a["vdim"] + 2 * Hb * b["dim"] + 2 * Hb * b["vdim"] + 2 * Hb
+                n_del = 2 * dl["kv_heads"] * dl["dim"] + 2 * Hd * dl["vdim"] + 2 * Hd
+                lin = 2 * 2.0 * W * (n_par + Ha * a["vdim"] + Hb * b["vdim"]) + 2 * 2.0 * W * (n_del + Hd * dl["vdim"])
+                flop_tok = lin + 4 * 2.0 * W * 3 * ff
+                flop_tok += 2 * 4.0 * Hb * b["dim"] * b["vdim"] + 2 * 6.0 * Hd * dl["dim"] * dl["vdim"]      # state updates + read-outs
+                att_flops = lambda S: 2 * 2.0 * Ha * (a["dim"] + a["vdim"]) * (S * (S + 1) // 2)
+                wbytes = flop_tok - (2 * 4.0 * Hb * b["dim"] * b["vdim"] + 2 * 6.0 * Hd * dl["dim"] * dl["vdim"])
+                state_bytes = 2 * 8.0 * (Hb * b["dim"] * b["vdim"] + Hd * dl["dim"] * dl["vdim"]) + 2 * 2.0 * ctx_len * Ga * (a["dim"] + a["vdim"])
+            else:
+                mo = MoeSpec(scale=2.5, **zs["moe"])
+                scale_ff = ff / float(mo.top * mo.ff + mo.shared_ff)   # the routed feed-forward at the dense one's active width
+                mo.ff, mo.shared_ff = int(mo.ff * scale_ff) // 64 * 64, int(mo.shared_ff * scale_ff) // 64 * 64
+                rot = RotarySpec(dims=zs["lat"]["rot_dim"], base=10000.0, factor=8.0, fast=32.0, slow=1.0, original=2048)
+                ret = lambda: MixerSpec(type="retention", decay=[1 - 2.0 ** (-5 - i % 4) for i in range(zs["ret"]["heads"])],
+                                        rot=RotarySpec(dims=zs["ret"]["dim"], base=10000.0), moe=mo, **zs["ret"])
+                lat = lambda: MixerSpec(type="latent_attention", scale=(zs["lat"]["dim"] + zs["lat"]["rot_dim"]) ** -0.5, rot=rot, moe=mo, **zs["lat"])
+                layers = [lat(), ret(), lat(), ret()]
+                cfg = Config(hidden_size=W, intermediate_size=0, vocab_size=vocab, num_hidden_layers=4, num_attention_heads=layers[0].heads,
+                             num_key_value_heads=layers[0].heads, rms_norm_eps=1e-6, head_dim=128, max_seq_len=mseq, block_kind="setodra",
+                             layers=layers, model_prefix="", embed_scale=1.0)
+                sd = make_mixer_checkpoint(cfg, "bf16", seed=5, device=env.dev, std=0.02)
+                r, la = zs["ret"], zs["lat"]
+                n_ret = 2 * r["heads"] * r["dim"] + 2 * r["heads"] * r["vdim"]
+                n_lat = la["heads"] * (la["dim"] + la["rot_dim"]) + la["kv_rank"] + la["rot_dim"]
+                ff_act = mo.top * mo.ff + mo.shared_ff
+                lat_up = 2.0 * la["heads"] * la["kv_rank"] * (la["dim"] + la["vdim"])
+                lin = 2 * 2.0 * W * (n_ret + r["heads"] * r["vdim"]) + 2 * (2.0 * W * (n_lat + la["heads"] * la["vdim"]) + lat_up)
+                flop_tok = lin + 4 * (2.0 * W * 3 * ff_act + 2.0 * W * (mo.experts + mo.identity)) + 2 * 4.0 * r["heads"] * r["dim"] * r["vdim"]
+                att_flops = lambda S: 2 * 2.0 * la["heads"] * (2 * la["kv_rank"] + la["rot_dim"]) * (S * (S + 1) // 2)
+                wbytes = lin + 4 * (2.0 * W * 3 * ff_act)
+                state_bytes = 2 * 8.0 * r["heads"] * r["dim"] * r["vdim"] + 2 * 2.0 * ctx_len * (la["kv_rank"] + la["rot_dim"])
+            t = _time_listed_model(env, cfg, sd, batch, seq, ctx_len, steps, reps, mseq)
+            del sd
+            torch.cuda.empty_cache()
+            launches += t["launches"]
+            M, ms, dms = batch * seq, t["prefill"]["ms"], t["decode"]["ms_per_token"]
+            flops = flop_tok * M + batch * att_flops(seq) + 2.0 * batch * vocab * W
+            dbytes = wbytes + state_bytes + 2.0 * vocab * W
+            row[arch] = {"prefill": {"tok_s": M / (ms / 1e3), "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+                                     "frac_of_tensor_peak": flops / (ms * 1e-3) / 1e12 / pk["tc"], "finite": t["prefill"]["finite"]},
+                         "decode": {"tok_s": 1e3 / dms, "ms_per_token": dms, "gb_s": dbytes / (dms * 1e-3) / 1e9,
+                                    "frac_of_hbm_peak": dbytes / (dms * 1e-3) / 1e9 / pk["hbm"], "launches_per_token": t["decode"]["launches_per_token"],
+                                    "finite": t["decode"]["finite"]}}
+        row["prefill_ratio"] = row["nuvarax"]["prefill"]["tok_s"] / row["closest"]["prefill"]["tok_s"]
+        row["decode_ratio"] = row["nuvarax"]["decode"]["tok_s"] / row["closest"]["decode"]["tok_s"]
+        out[name] = row
+    head = out[sizes[-1]]
+    return {"metric": f"nuvarax prefill tok/s (4 layers, width {head['size']['width']}, bf16, bs={batch} x {seq})", "value": head["nuvarax"]["prefill"]["tok_s"],
+            "unit": "tok/s", "ms_per_step": head["nuvarax"]["prefill"]["ms"], "steps": reps, "warmup": 1, "gpu_launches": int(launches),
+            "config": {"workload": f"Nuvarax vs Setodra at equal width, layer count and active feed-forward width, 4 layers, bf16, prefill bs={batch} x {seq}, "
+                                   f"decode bs=1 at {ctx_len} context x {steps} steps", "l2": "prefill activations / decode weights exceed L2"},
+            "peaks": {"tensor_tflops": pk["tc"], "hbm_gbs": pk["hbm"], "source": pk["src"]}, "sizes": out}
+
+
 # ------------------------------------------------------------------------------------------------
 def run_cuda(args):
     env = Env(args)
@@ -1158,6 +1298,16 @@ def run_cuda(args):
                 env.sampler.start()
             sizes = tuple((args.sizes if args.sizes != "2k,4k,4k-hd64" else "1k,2k").split(","))
             line = setodra_leg(env, sizes=sizes, batch=args.pf_batch, seq=args.pf_seq, steps=max(4, min(args.steps, 64)))
+            line["clocks"] = env.sampler.stop() if env.sampler else None
+            line.update({"n_gpus": 1, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic"})
+            emit(line)
+        return
+    if args.workload == "nuvarax":
+        if rank == 0:
+            if env.sampler:
+                env.sampler.start()
+            sizes = tuple((args.sizes if args.sizes != "2k,4k,4k-hd64" else "1k,2k").split(","))
+            line = nuvarax_leg(env, sizes=sizes, batch=args.pf_batch, seq=args.pf_seq, steps=max(4, min(args.steps, 64)))
             line["clocks"] = env.sampler.stop() if env.sampler else None
             line.update({"n_gpus": 1, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic"})
             emit(line)
@@ -1235,9 +1385,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--model", default="8b", choices=["8b", "70b"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "nigenex", "setodra"])
-    ap.add_argument("--pf-batch", type=int, default=4, help="--workload setodra: batch rows of the prefill step")
-    ap.add_argument("--pf-seq", type=int, default=4096, help="--workload setodra: tokens per row of the prefill step")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "nigenex", "setodra", "nuvarax"])
+    ap.add_argument("--pf-batch", type=int, default=4, help="--workload setodra / nuvarax: batch rows of the prefill step")
+    ap.add_argument("--pf-seq", type=int, default=4096, help="--workload setodra / nuvarax: tokens per row of the prefill step")
     ap.add_argument("--sizes", default="2k,4k,4k-hd64", help="--workload nigenex: which of NIGENEX_SIZES to run")
     ap.add_argument("--extras", default="auto", choices=["auto", "none", "all"],
                     help="auto: config0 + config4 at N=1, config3 (70B) at N=8; none: the headline only")

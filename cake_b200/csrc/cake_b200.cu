@@ -247,6 +247,7 @@ struct cake_b200_cache {
   // side mixer; rec_aux: the normaliser and running maximum of a matrix memory [batch, heads, dk + 1] fp32; canon_hist: the
   // last canon_taps - 1 normed inputs of the block [batch, taps - 1, hidden] fp32
   std::vector<float *> rec_aux, canon_hist;
+  std::vector<void *> vt;   // talking attention on the tensor cores: the values once more, [batch, kv_heads, vdim, cap_t] with positions innermost
   // cake_b200_embed_at: the last token of every batch row and the position the embedding has reached
   std::vector<uint32_t> last_tok;
   int embed_len = 0;
@@ -800,6 +801,7 @@ extern "C" int cake_b200_cache_create(cake_b200_ctx *c, int batch, int max_seq, 
   k->kv_heads.assign(slots, 0);
   k->kv_hd.assign(slots, 0);
   k->rec_aux.assign(slots, nullptr);
+  k->vt.assign(slots, nullptr);
   k->canon_hist.assign(c->cfg.n_layers, nullptr);
   k->last_tok.assign(batch, 0);
   k->shift_state[0].assign(c->cfg.n_layers, nullptr);
@@ -861,6 +863,8 @@ extern "C" void cake_b200_cache_free(cake_b200_cache *k) {
   for (void *p : k->conv_hist)
     if (p) cudaFree(p);
   for (float *p : k->rec_aux)
+    if (p) cudaFree(p);
+  for (void *p : k->vt)
     if (p) cudaFree(p);
   for (float *p : k->canon_hist)
     if (p) cudaFree(p);
@@ -1971,6 +1975,16 @@ static int load_mixer_ext(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer
   return CAKE_B200_OK;
 }
 
+// Long portions of a talking-attention layer in 16-bit D run as matrix products on the tensor cores when the tiles cover the
+// shapes: scores = q . keys^T (K = dim), output = weights . values (N = vdim).
+static bool talk_on_tc(const cake_b200_ctx *c, const cake_b200_block *b) {
+  static const bool no_tc = []() { const char *e = getenv("CAKE_B200_NO_TC"); return e && e[0] == '1'; }();
+  const cake_b200_mixer_spec &sp = b->ms;
+  return !no_tc && c->cfg.dtype != CAKE_B200_F32 && sp.kind == CAKE_B200_MIX_TALKING_ATTENTION && sp.dim % TC_BK == 0 && sp.vdim % TC_BN == 0;
+}
+constexpr int TALK_TC_MIN_ROWS = 1024;          // (token, head) rows of a step below which the per-row kernel runs
+constexpr size_t TALK_TC_SCORE_BYTES = 512u << 20;  // bound of the fp32 score block: sets the tokens per block
+
 // cache entries of one mixer of an ext block at `slot` (block_idx, or n_layers + block_idx for the side mixer)
 static int cache_ensure_sub(cake_b200_cache *k, int slot, const cake_b200_block *b) {
   cake_b200_ctx *c = k->ctx;
@@ -1983,6 +1997,7 @@ static int cache_ensure_sub(cake_b200_cache *k, int slot, const cake_b200_block 
   if (sp.kind == CAKE_B200_MIX_TALKING_ATTENTION) {
     CU(cudaMalloc(&k->k[slot], (size_t)k->batch * G * k->cap * sp.dim * c->es + 16));
     CU(cudaMalloc(&k->v[slot], (size_t)k->batch * G * k->cap * sp.vdim * c->es + 16));
+    if (talk_on_tc(c, b)) CU(cudaMalloc(&k->vt[slot], (size_t)k->batch * G * sp.vdim * latent_cap_t(k->cap) * c->es + 16));
   } else {
     CU(cudaMalloc(&k->rec_state[slot], (size_t)k->batch * width * sizeof(float)));
     if (sp.kind == CAKE_B200_MIX_DELTA && sp.conv > 1)
@@ -2005,18 +2020,31 @@ static int cache_ensure_ext(cake_b200_cache *k, int layer, const cake_b200_block
 
 // scratch of one mixer of an ext block
 struct SubScratch {
-  void *att, *conv;
-  float *o32, *qn, *kn, *f1, *f2, *f3, *part, *y;
-  int nsplit;
+  void *att, *conv, *qh, *pw, *oh;
+  float *o32, *qn, *kn, *f1, *f2, *f3, *part, *y, *scores, *stats;
+  int nsplit, tc_tok;
 };
 constexpr int TALK_SPLIT_MAX = 64;
-template <typename Take> static SubScratch sub_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, int n_keys, Take &&take) {
+template <typename Take> static SubScratch sub_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, int S, int n_keys, Take &&take) {
   SubScratch s{};
   const cake_b200_mixer_spec &sp = b->ms;
   const size_t es = c->es, inner = (size_t)sp.heads * sp.vdim, G = sp.kv_heads;
   s.att = take(M * inner * es);
   s.y = (float *)take(M * c->cfg.hidden * sizeof(float));
   if (sp.kind == CAKE_B200_MIX_TALKING_ATTENTION) {
+    if (talk_on_tc(c, b) && (size_t)S * sp.heads >= TALK_TC_MIN_ROWS) {  // blocks of tc_tok tokens of one batch row as matrix products
+      const size_t kp = ((size_t)n_keys + TC_BN - 1) / TC_BN * TC_BN;
+      size_t nt = TALK_TC_SCORE_BYTES / (sp.heads * kp * sizeof(float)) / TC_BM * TC_BM;
+      nt = std::min<size_t>((size_t)S, std::max<size_t>(nt, TC_BM));
+      s.tc_tok = (int)nt;
+      const size_t rows = nt * sp.heads;
+      s.qh = take(rows * sp.dim * es);
+      s.scores = (float *)take(rows * kp * sizeof(float));
+      s.pw = take(rows * 2 * kp * es);
+      s.stats = (float *)take(rows * 2 * sizeof(float));
+      s.oh = take(rows * sp.vdim * es);
+      return s;
+    }
     // steps of a few rows over many keys: split the keys so that the step fills the chip
     if (M <= 32 && n_keys >= 256) {
       s.nsplit = (int)std::min<size_t>(TALK_SPLIT_MAX, std::min<size_t>((n_keys + 127) / 128, (2 * (size_t)c->sm_count + M - 1) / M));
@@ -2041,7 +2069,7 @@ struct ExtScratch {
   SubScratch a, b;
   size_t total;
 };
-static ExtScratch ext_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, char *base, int n_keys) {
+static ExtScratch ext_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, char *base, int S, int n_keys) {
   ExtScratch s{};
   size_t off = 0;
   auto take = [&](size_t bytes) -> void * {
@@ -2053,8 +2081,8 @@ static ExtScratch ext_scratch(const cake_b200_ctx *c, const cake_b200_block *b, 
   s.h = take(M * H * es);
   if (b->ms.canon_taps > 0) s.h32 = (float *)take(M * H * sizeof(float));
   s.proj = take(M * b->n_in_pad * es);
-  s.a = sub_scratch(c, b, M, n_keys, take);
-  if (b->side) s.b = sub_scratch(c, b->side, M, n_keys, take);
+  s.a = sub_scratch(c, b, M, S, n_keys, take);
+  if (b->side) s.b = sub_scratch(c, b->side, M, S, n_keys, take);
   if (b->ms.dense_ff > 0) s.act = take(M * (size_t)b->ms.dense_ff * es);
   s.total = off;
   return s;
@@ -2093,9 +2121,40 @@ static int run_sub_mixer(cake_b200_ctx *c, const cake_b200_block *b, cake_b200_c
   } else if (sp.kind == CAKE_B200_MIX_TALKING_ATTENTION) {
     RC(launch_pdl(c, rows_to_cache_kernel<T>, dim3(M), dim3(128), 0, proj, (T *)kc->k[slot], S, ldp, b->pc[1], G, sp.dim, kc->cap, pos0));
     RC(launch_pdl(c, rows_to_cache_kernel<T>, dim3(M), dim3(128), 0, proj, (T *)kc->v[slot], S, ldp, b->pc[2], G, sp.vdim, kc->cap, pos0));
-    mx::TalkAttn ta{proj + b->pc[0], ldp, kc->k[slot], kc->v[slot], b->pc[3] >= 0 ? proj + b->pc[3] : nullptr, ldp, b->m_bias, b->m_bias_len, b->m_talk,
-                    w.att, B, S, sp.heads, G, sp.dim, sp.vdim, kc->cap, pos0, sp.scale, w.part, w.nsplit};
-    MX(mx::talk_attention(st, dt, ta, lc));
+    const int cap_t = latent_cap_t(kc->cap);
+    if (kc->vt[slot]) MX(mx::values_transposed_append(st, dt, proj, ldp, b->pc[2], kc->vt[slot], B, S, G, sp.vdim, cap_t, pos0, lc));
+    if (w.scores && kc->vt[slot]) {
+      // blocks of tc_tok tokens: per key head scores = q rows . keys^T on the keys the block's last token sees, softmax + head
+      // mixing into w_hi | w_lo, per key head output = [w_hi | w_lo] . values with the values' k coordinate wrapping at kp
+      const int grp = sp.heads / G;
+      for (int bb = 0; bb < B; bb++)
+        for (int t0 = 0; t0 < S; t0 += w.tc_tok) {
+          const int n = std::min(w.tc_tok, S - t0), nk = pos0 + t0 + n, kp = round_up(nk, TC_BN);
+          const T *pr = proj + ((size_t)bb * S + t0) * ldp;
+          MX(mx::rows_by_head(st, dt, pr + b->pc[0], ldp, w.qh, n, sp.heads, sp.dim, lc));
+          for (int g = 0; g < G; g++) {
+            TcExtra xs;
+            xs.w_rows = nk;   // rows past the visible keys read as zeros
+            RC((listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, (const T *)w.qh + (size_t)g * grp * n * sp.dim, (const T *)kc->k[slot] + ((size_t)bb * G + g) * kc->cap * sp.dim,
+                                                   nullptr, w.scores + (size_t)g * grp * n * kp, grp * n, kp, sp.dim, 0, 0, 0.f, xs)));
+          }
+          mx::TalkSoftmax sm{w.scores, w.pw, w.stats, b->m_bias, b->m_bias_len, b->m_talk, n, sp.heads, kp, pos0 + t0, sp.scale};
+          MX(mx::talk_softmax(st, dt, sm, lc));
+          for (int g = 0; g < G; g++) {
+            TcExtra xv;
+            xv.b_kwrap = kp;
+            xv.w_cols = nk;
+            xv.w_ld = cap_t;
+            RC((listed_gemm_tc<T, TCE_PLAIN>(c, (const T *)w.pw + (size_t)g * grp * n * 2 * kp, (const T *)kc->vt[slot] + ((size_t)bb * G + g) * sp.vdim * cap_t, nullptr,
+                                             (T *)w.oh + (size_t)g * grp * n * sp.vdim, grp * n, sp.vdim, 2 * kp, 0, 0, 0.f, xv)));
+          }
+          MX(mx::rows_to_tokens(st, dt, w.oh, b->pc[3] >= 0 ? pr + b->pc[3] : nullptr, ldp, (T *)w.att + ((size_t)bb * S + t0) * inner, inner, n, sp.heads, sp.vdim, lc));
+        }
+    } else {
+      mx::TalkAttn ta{proj + b->pc[0], ldp, kc->k[slot], kc->v[slot], b->pc[3] >= 0 ? proj + b->pc[3] : nullptr, ldp, b->m_bias, b->m_bias_len, b->m_talk,
+                      w.att, B, S, sp.heads, G, sp.dim, sp.vdim, kc->cap, pos0, sp.scale, w.part, w.nsplit};
+      MX(mx::talk_attention(st, dt, ta, lc));
+    }
   } else {
     const float qs = 1.0f / sqrtf((float)sp.dim);
     mx::GatePrep gp{proj + b->pc[0], proj + b->pc[1], ldp, proj + b->pc[4], proj + b->pc[5], ldp, b->m_ib, b->m_fb, kc->rec_aux[slot], w.f1, w.f2, w.f3,
@@ -2118,7 +2177,7 @@ static int enqueue_ext_layer(cake_b200_ctx *c, const cake_b200_block *b, int l, 
   const int M = B * S, H = c->cfg.hidden, dt = c->cfg.dtype, nl = (int)kc->len.size();
   const float eps = c->cfg.rms_eps;
   cudaStream_t st = c->stream;
-  const ExtScratch w = ext_scratch(c, b, (size_t)M, (char *)c->mx_ws, pos0 + S);
+  const ExtScratch w = ext_scratch(c, b, (size_t)M, (char *)c->mx_ws, S, pos0 + S);
   // 1. h = norm1(x), the input convolution, every projection of the mixer(s) in one product
   mx::RmsRows n1{cur, b->ln1, sp.norm_offset, sp.canon_taps > 0 ? w.h32 : nullptr, sp.canon_taps > 0 ? nullptr : w.h, M, H, eps};
   MX(mx::rms_rows(st, dt, n1, lc));
@@ -2255,7 +2314,7 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
   const int H = c->cfg.hidden, M = B * S, dt = c->cfg.dtype;
   size_t need = 0;
   for (int i = 0; i < n; i++) {
-    need = std::max(need, blocks[i]->ext ? ext_scratch(c, blocks[i], (size_t)M, nullptr, pos0 + S).total
+    need = std::max(need, blocks[i]->ext ? ext_scratch(c, blocks[i], (size_t)M, nullptr, S, pos0 + S).total
                                          : mixer_scratch(c, blocks[i], (size_t)M, nullptr, S, pos0 + S).total);
     if (blocks[i]->m_cos && pos0 + S > blocks[i]->m_rope_rows)
       return fail(CAKE_B200_ESTATE, "position %d exceeds the rotation table (%d rows = the ctx's max_seq)", pos0 + S, blocks[i]->m_rope_rows);

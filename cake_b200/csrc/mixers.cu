@@ -1340,39 +1340,105 @@ int delta_prep(cudaStream_t st, int dtype, const DeltaPrep &p, uint64_t *launche
   MX_DONE(1);
 }
 
-// A thread owns one column of the state (dk values): the columns are independent, u and o of a column need only that column.
-// DKP > 0: the column sits in DKP registers (dk <= DKP, the rest zero); DKP == 0: in shared memory, any dk.  Tokens come in
-// chunks of DR_TT whose q, k, v, beta and g are staged in shared memory once per CTA (blockDim.x columns of one head).
-constexpr int DR_TT = 16;
-template <typename T, int DKP>
-__global__ void __launch_bounds__(128) delta_rule_kernel(const DeltaRule p) {
+// The columns of the state are independent: u and o of a column need only that column.  Tokens come in chunks of DR_TT whose
+// q, k, v, beta and g are staged in shared memory once per CTA (DR_CB columns of one head).
+// Register form (dk <= R * RS): RS adjacent lanes share a column, lane s of them keeps rows s R .. s R + R - 1 in registers;
+// S^T k and S^T q are R products per lane and log2(RS) shuffles.
+constexpr int DR_TT = 16, DR_CB = 32;
+template <typename T, int R, int RS>
+__global__ void __launch_bounds__(DR_CB * RS) delta_rule_kernel(const DeltaRule p) {
   extern __shared__ float sm[];
-  const int CB = blockDim.x, dk = p.dk, dv = p.dv;
-  const int ld = DKP > 0 ? DKP : (dk + 3) / 4 * 4;   // row length of the staged q / k
-  float *qs = sm, *ks = qs + DR_TT * ld, *vs = ks + DR_TT * ld, *gs = vs + DR_TT * CB, *bs = gs + DR_TT, *Ss = bs + DR_TT;
-  const int ncb = (dv + CB - 1) / CB, h = blockIdx.x / ncb, cb = blockIdx.x % ncb, b = blockIdx.y;
-  const int col = cb * CB + threadIdx.x;
+  constexpr int ld = R * RS, NTH = DR_CB * RS;
+  float *qs = sm, *ks = qs + DR_TT * ld, *vs = ks + DR_TT * ld, *gs = vs + DR_TT * DR_CB, *bs = gs + DR_TT;
+  const int dk = p.dk, dv = p.dv;
+  const int ncb = (dv + DR_CB - 1) / DR_CB, h = blockIdx.x / ncb, cb = blockIdx.x % ncb, b = blockIdx.y;
+  const int s = threadIdx.x % RS, cl = threadIdx.x / RS, col = cb * DR_CB + cl;
   const bool active = col < dv;
   const int kvh = h / (p.heads / p.kv_heads), qk_ld = p.kv_heads * dk;
-  float *gstate = p.state + ((size_t)b * p.heads + h) * dk * dv + col;
-  float St[DKP > 0 ? DKP : 1];
-  if (DKP > 0) {
+  float *gstate = p.state + (((size_t)b * p.heads + h) * dk + (size_t)s * R) * dv + col;
+  float St[R];
 #pragma unroll
-    for (int r = 0; r < DKP; r++) St[r] = (active && r < dk && p.pos0 > 0) ? gstate[(size_t)r * dv] : 0.f;
-  } else {
-    for (int r = 0; r < dk; r++) Ss[r * CB + threadIdx.x] = (active && p.pos0 > 0) ? gstate[(size_t)r * dv] : 0.f;
-  }
+  for (int r = 0; r < R; r++) St[r] = (active && s * R + r < dk && p.pos0 > 0) ? gstate[(size_t)r * dv] : 0.f;
   for (int t0 = 0; t0 < p.S; t0 += DR_TT) {
     const int nt = min(DR_TT, p.S - t0);
     const size_t m0 = (size_t)b * p.S + t0;
     __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * ld; idx += CB) {
+    for (int idx = threadIdx.x; idx < nt * ld; idx += NTH) {
       const int tt = idx / ld, r = idx % ld;
       qs[idx] = r < dk ? p.qn[(m0 + tt) * qk_ld + (size_t)kvh * dk + r] : 0.f;
       ks[idx] = r < dk ? p.kn[(m0 + tt) * qk_ld + (size_t)kvh * dk + r] : 0.f;
     }
-    for (int idx = threadIdx.x; idx < nt * CB; idx += CB) {
-      const int tt = idx / CB, j = cb * CB + idx % CB;
+    for (int idx = threadIdx.x; idx < nt * DR_CB; idx += NTH) {
+      const int tt = idx / DR_CB, j = cb * DR_CB + idx % DR_CB;
+      vs[idx] = j < dv ? DT<T>::to_f(reinterpret_cast<const T *>(p.v)[(m0 + tt) * p.ldv + (size_t)h * dv + j]) : 0.f;
+    }
+    if ((int)threadIdx.x < nt) {
+      gs[threadIdx.x] = p.g[(m0 + threadIdx.x) * p.heads + h];
+      bs[threadIdx.x] = p.beta[(m0 + threadIdx.x) * p.heads + h];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; tt++) {
+      const float g = gs[tt];
+      const float *kq = ks + tt * ld + s * R, *qq = qs + tt * ld + s * R;
+      float kr[R];
+      float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        const float4 k4 = *reinterpret_cast<const float4 *>(kq + r);
+        kr[r] = k4.x; kr[r + 1] = k4.y; kr[r + 2] = k4.z; kr[r + 3] = k4.w;
+        St[r] *= g; d0 = fmaf(St[r], k4.x, d0);
+        St[r + 1] *= g; d1 = fmaf(St[r + 1], k4.y, d1);
+        St[r + 2] *= g; d0 = fmaf(St[r + 2], k4.z, d0);
+        St[r + 3] *= g; d1 = fmaf(St[r + 3], k4.w, d1);
+      }
+      float d = d0 + d1;
+#pragma unroll
+      for (int o = RS / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      const float u = bs[tt] * (vs[tt * DR_CB + cl] - d);
+      float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        const float4 q4 = *reinterpret_cast<const float4 *>(qq + r);
+        St[r] = fmaf(kr[r], u, St[r]); o0 = fmaf(St[r], q4.x, o0);
+        St[r + 1] = fmaf(kr[r + 1], u, St[r + 1]); o1 = fmaf(St[r + 1], q4.y, o1);
+        St[r + 2] = fmaf(kr[r + 2], u, St[r + 2]); o0 = fmaf(St[r + 2], q4.z, o0);
+        St[r + 3] = fmaf(kr[r + 3], u, St[r + 3]); o1 = fmaf(St[r + 3], q4.w, o1);
+      }
+      float o = o0 + o1;
+#pragma unroll
+      for (int x = RS / 2; x > 0; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+      if (active && s == 0) p.o[(m0 + tt) * ((size_t)p.heads * dv) + (size_t)h * dv + col] = o;
+    }
+  }
+  if (active) {
+#pragma unroll
+    for (int r = 0; r < R; r++)
+      if (s * R + r < dk) gstate[(size_t)r * dv] = St[r];
+  }
+}
+// Shared-memory form for any dk: a thread owns one column, which sits in shared memory.
+template <typename T>
+__global__ void __launch_bounds__(DR_CB) delta_rule_smem_kernel(const DeltaRule p) {
+  extern __shared__ float sm[];
+  const int dk = p.dk, dv = p.dv, ld = (dk + 3) / 4 * 4;
+  float *qs = sm, *ks = qs + DR_TT * ld, *vs = ks + DR_TT * ld, *gs = vs + DR_TT * DR_CB, *bs = gs + DR_TT, *Ss = bs + DR_TT;
+  const int ncb = (dv + DR_CB - 1) / DR_CB, h = blockIdx.x / ncb, cb = blockIdx.x % ncb, b = blockIdx.y;
+  const int col = cb * DR_CB + threadIdx.x;
+  const bool active = col < dv;
+  const int kvh = h / (p.heads / p.kv_heads), qk_ld = p.kv_heads * dk;
+  float *gstate = p.state + ((size_t)b * p.heads + h) * dk * dv + col;
+  for (int r = 0; r < dk; r++) Ss[r * DR_CB + threadIdx.x] = (active && p.pos0 > 0) ? gstate[(size_t)r * dv] : 0.f;
+  for (int t0 = 0; t0 < p.S; t0 += DR_TT) {
+    const int nt = min(DR_TT, p.S - t0);
+    const size_t m0 = (size_t)b * p.S + t0;
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * ld; idx += DR_CB) {
+      const int tt = idx / ld, r = idx % ld;
+      qs[idx] = r < dk ? p.qn[(m0 + tt) * qk_ld + (size_t)kvh * dk + r] : 0.f;
+      ks[idx] = r < dk ? p.kn[(m0 + tt) * qk_ld + (size_t)kvh * dk + r] : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < nt * DR_CB; idx += DR_CB) {
+      const int tt = idx / DR_CB, j = cb * DR_CB + idx % DR_CB;
       vs[idx] = j < dv ? DT<T>::to_f(reinterpret_cast<const T *>(p.v)[(m0 + tt) * p.ldv + (size_t)h * dv + j]) : 0.f;
     }
     if ((int)threadIdx.x < nt) {
@@ -1383,145 +1449,160 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(const DeltaRule p) {
     for (int tt = 0; tt < nt; tt++) {
       const float g = gs[tt];
       const float *kq = ks + tt * ld, *qq = qs + tt * ld;
-      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-      if (DKP > 0) {
-#pragma unroll
-        for (int r = 0; r < DKP; r += 4) {
-          const float4 k4 = *reinterpret_cast<const float4 *>(kq + r);
-          St[r] *= g; d0 = fmaf(St[r], k4.x, d0);
-          St[r + 1] *= g; d1 = fmaf(St[r + 1], k4.y, d1);
-          St[r + 2] *= g; d2 = fmaf(St[r + 2], k4.z, d2);
-          St[r + 3] *= g; d3 = fmaf(St[r + 3], k4.w, d3);
-        }
-      } else {
-        for (int r = 0; r < dk; r++) {
-          const float sv = Ss[r * CB + threadIdx.x] * g;
-          Ss[r * CB + threadIdx.x] = sv;
-          d0 = fmaf(sv, kq[r], d0);
-        }
+      float d = 0.f;
+      for (int r = 0; r < dk; r++) {
+        const float sv = Ss[r * DR_CB + threadIdx.x] * g;
+        Ss[r * DR_CB + threadIdx.x] = sv;
+        d = fmaf(sv, kq[r], d);
       }
-      const float u = bs[tt] * (vs[tt * CB + threadIdx.x] - ((d0 + d1) + (d2 + d3)));
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-      if (DKP > 0) {
-#pragma unroll
-        for (int r = 0; r < DKP; r += 4) {
-          const float4 k4 = *reinterpret_cast<const float4 *>(kq + r), q4 = *reinterpret_cast<const float4 *>(qq + r);
-          St[r] = fmaf(k4.x, u, St[r]); o0 = fmaf(St[r], q4.x, o0);
-          St[r + 1] = fmaf(k4.y, u, St[r + 1]); o1 = fmaf(St[r + 1], q4.y, o1);
-          St[r + 2] = fmaf(k4.z, u, St[r + 2]); o2 = fmaf(St[r + 2], q4.z, o2);
-          St[r + 3] = fmaf(k4.w, u, St[r + 3]); o3 = fmaf(St[r + 3], q4.w, o3);
-        }
-      } else {
-        for (int r = 0; r < dk; r++) {
-          const float sv = fmaf(kq[r], u, Ss[r * CB + threadIdx.x]);
-          Ss[r * CB + threadIdx.x] = sv;
-          o0 = fmaf(sv, qq[r], o0);
-        }
+      const float u = bs[tt] * (vs[tt * DR_CB + threadIdx.x] - d);
+      float o = 0.f;
+      for (int r = 0; r < dk; r++) {
+        const float sv = fmaf(kq[r], u, Ss[r * DR_CB + threadIdx.x]);
+        Ss[r * DR_CB + threadIdx.x] = sv;
+        o = fmaf(sv, qq[r], o);
       }
-      if (active) p.o[(m0 + tt) * ((size_t)p.heads * dv) + (size_t)h * dv + col] = (o0 + o1) + (o2 + o3);
+      if (active) p.o[(m0 + tt) * ((size_t)p.heads * dv) + (size_t)h * dv + col] = o;
     }
   }
-  if (active) {
-    if (DKP > 0) {
-#pragma unroll
-      for (int r = 0; r < DKP; r++)
-        if (r < dk) gstate[(size_t)r * dv] = St[r];
-    } else {
-      for (int r = 0; r < dk; r++) gstate[(size_t)r * dv] = Ss[r * CB + threadIdx.x];
-    }
-  }
+  if (active)
+    for (int r = 0; r < dk; r++) gstate[(size_t)r * dv] = Ss[r * DR_CB + threadIdx.x];
 }
-template <typename T, int DKP> static cudaError_t launch_delta_rule(cudaStream_t st, const DeltaRule &p) {
-  // columns per CTA: 64 when that still gives every SM a CTA, else 32
-  int CB = (p.dv % 64 == 0 && (long)p.B * p.heads * (p.dv / 64) >= 148) ? 64 : 32;
-  const int ld = DKP > 0 ? DKP : (p.dk + 3) / 4 * 4;
-  const size_t smem = ((size_t)2 * DR_TT * ld + (size_t)DR_TT * CB + 2 * DR_TT + (DKP > 0 ? 0 : (size_t)p.dk * CB)) * sizeof(float);
+template <typename T, int R, int RS> static cudaError_t launch_delta_rule(cudaStream_t st, const DeltaRule &p) {
+  const size_t smem = ((size_t)2 * DR_TT * R * RS + (size_t)DR_TT * DR_CB + 2 * DR_TT) * sizeof(float);
+  delta_rule_kernel<T, R, RS><<<dim3(p.heads * ((p.dv + DR_CB - 1) / DR_CB), p.B), DR_CB * RS, smem, st>>>(p);
+  return cudaSuccess;
+}
+template <typename T> static cudaError_t launch_delta_rule_smem(cudaStream_t st, const DeltaRule &p) {
+  const int ld = (p.dk + 3) / 4 * 4;
+  const size_t smem = ((size_t)2 * DR_TT * ld + (size_t)DR_TT * DR_CB + 2 * DR_TT + (size_t)p.dk * DR_CB) * sizeof(float);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<T, DKP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(delta_rule_smem_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  delta_rule_kernel<T, DKP><<<dim3(p.heads * ((p.dv + CB - 1) / CB), p.B), CB, smem, st>>>(p);
+  delta_rule_smem_kernel<T><<<dim3(p.heads * ((p.dv + DR_CB - 1) / DR_CB), p.B), DR_CB, smem, st>>>(p);
   return cudaSuccess;
 }
 int delta_rule(cudaStream_t st, int dtype, const DeltaRule &p, uint64_t *launches) {
   if (p.B < 1 || p.S < 1 || p.heads < 1 || p.kv_heads < 1 || p.heads % p.kv_heads || p.dk < 1 || p.dv < 1) return (int)cudaErrorInvalidValue;
   cudaError_t e = cudaSuccess;
   MX_DISPATCH(dtype, {
-    if (p.dk <= 16) e = launch_delta_rule<T, 16>(st, p);
-    else if (p.dk <= 32) e = launch_delta_rule<T, 32>(st, p);
-    else if (p.dk <= 64) e = launch_delta_rule<T, 64>(st, p);
-    else if (p.dk <= 96) e = launch_delta_rule<T, 96>(st, p);
-    else if (p.dk <= 128) e = launch_delta_rule<T, 128>(st, p);
-    else e = launch_delta_rule<T, 0>(st, p);
+    if (p.dk <= 16) e = launch_delta_rule<T, 16, 1>(st, p);
+    else if (p.dk <= 32) e = launch_delta_rule<T, 16, 2>(st, p);
+    else if (p.dk <= 64) e = launch_delta_rule<T, 16, 4>(st, p);
+    else if (p.dk <= 128) e = launch_delta_rule<T, 16, 8>(st, p);
+    else if (p.dk <= 256) e = launch_delta_rule<T, 32, 8>(st, p);
+    else e = launch_delta_rule_smem<T>(st, p);
   });
   if (e != cudaSuccess) return (int)e;
   MX_DONE(1);
 }
 
 // ---------------------------------------------------------------------------------------------- exponential gates
-// One warp per (head, batch row) walks the tokens in order; lane l owns the entries l, l + 32, ... of the normaliser n.
-constexpr int GP_TT = 16;
+// One CTA of four warps per (head, batch row) walks the tokens in chunks of 32.  All threads stage the chunk's q and k; warp 0
+// computes the chunk's log gates (a lane per token), then the running maximum as a prefix scan: m' = max(f + m, i) composes as
+// (f1, i1) then (f2, i2) = (f1 + f2, max(f2 + i1, i2)); then it walks the tokens: lane l owns the entries l, l + 32, ... of n.
+constexpr int GP_TT = 32, GP_THREADS = 128;
 template <typename T>
-__global__ void __launch_bounds__(32) gate_prep_kernel(const GatePrep p) {
+__global__ void __launch_bounds__(GP_THREADS) gate_prep_kernel(const GatePrep p) {
   extern __shared__ float sm[];
-  const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x, dk = p.dk;
-  float *ns = sm, *ks = ns + dk, *qs = ks + GP_TT * dk, *lis = qs + GP_TT * dk, *lfs = lis + GP_TT;
+  const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, dk = p.dk;
+  float *ns = sm, *ks = ns + dk, *qs = ks + GP_TT * dk, *as = qs + GP_TT * dk, *bs = as + GP_TT, *es = bs + GP_TT;
   float *aux = p.aux + ((size_t)b * p.heads + h) * (dk + 1);
-  for (int r = lane; r < dk; r += 32) ns[r] = p.pos0 > 0 ? aux[r] : 0.f;
-  float mx = p.pos0 > 0 ? aux[dk] : 0.f;
+  if (warp == 0)
+    for (int r = lane; r < dk; r += 32) ns[r] = p.pos0 > 0 ? aux[r] : 0.f;
+  float mx = p.pos0 > 0 ? aux[dk] : 0.f;   // warp 0 carries it
   const float ib = DT<T>::to_f(reinterpret_cast<const T *>(p.i_b)[h]), fb = DT<T>::to_f(reinterpret_cast<const T *>(p.f_b)[h]);
+  const bool vec = sizeof(T) == 2 && (dk & 7) == 0 && (p.ld & 7) == 0 && (((uintptr_t)p.q | (uintptr_t)p.k) & 15) == 0;
   for (int t0 = 0; t0 < p.S; t0 += GP_TT) {
     const int nt = min(GP_TT, p.S - t0);
     const size_t m0 = (size_t)b * p.S + t0;
-    __syncwarp();
-    for (int idx = lane; idx < nt * dk; idx += 32) {
-      const int tt = idx / dk, r = idx % dk;
-      ks[idx] = DT<T>::to_f(reinterpret_cast<const T *>(p.k)[(m0 + tt) * p.ld + (size_t)h * dk + r]);
-      qs[idx] = DT<T>::to_f(reinterpret_cast<const T *>(p.q)[(m0 + tt) * p.ld + (size_t)h * dk + r]);
-    }
-    if (lane < nt) {
-      const float ir = DT<T>::to_f(reinterpret_cast<const T *>(p.iraw)[(m0 + lane) * p.ldg + h]) + ib;
-      const float fr = DT<T>::to_f(reinterpret_cast<const T *>(p.fraw)[(m0 + lane) * p.ldg + h]) + fb;
-      lis[lane] = p.cap * tanhf(ir / p.cap);
-      const float z = p.cap * tanhf(fr / p.cap);
-      lfs[lane] = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));  // log sigmoid(z)
-    }
-    __syncwarp();
-    for (int tt = 0; tt < nt; tt++) {
-      const float li = lis[tt], lf = lfs[tt];
-      const float mn = fmaxf(lf + mx, li);
-      const float a = expf(lf + mx - mn), bb = expf(li - mn);
-      float dot = 0.f;
-      for (int r = lane; r < dk; r += 32) {
-        const float nv = fmaf(a, ns[r], bb * ks[tt * dk + r]);
-        ns[r] = nv;
-        dot = fmaf(nv, qs[tt * dk + r], dot);
+    __syncthreads();   // the previous chunk has been consumed
+    if (vec) {
+      typedef typename Bits16<T>::type B;
+      const int c8 = dk / 8;
+      for (int idx = threadIdx.x; idx < nt * c8; idx += GP_THREADS) {
+        const int tt = idx / c8, r = (idx % c8) * 8;
+        float f[8];
+        unpack8<B>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.k) + (m0 + tt) * p.ld + (size_t)h * dk + r), f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) ks[tt * dk + r + e] = f[e];
+        unpack8<B>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.q) + (m0 + tt) * p.ld + (size_t)h * dk + r), f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) qs[tt * dk + r + e] = f[e];
       }
-      dot = warp_sum(dot) * p.qscale;
-      if (lane == 0) {
-        const size_t o = (m0 + tt) * p.heads + h;
-        p.a[o] = a;
-        p.b[o] = bb;
-        p.div[o] = (fmaxf(fabsf(dot), expf(-mn)) + 1e-6f) / p.qscale;
+    } else {
+      for (int idx = threadIdx.x; idx < nt * dk; idx += GP_THREADS) {
+        const int tt = idx / dk, r = idx % dk;
+        ks[idx] = DT<T>::to_f(reinterpret_cast<const T *>(p.k)[(m0 + tt) * p.ld + (size_t)h * dk + r]);
+        qs[idx] = DT<T>::to_f(reinterpret_cast<const T *>(p.q)[(m0 + tt) * p.ld + (size_t)h * dk + r]);
       }
-      mx = mn;
+    }
+    if (warp == 0) {
+      float li = -INFINITY, lf = 0.f;   // tokens past the chunk's end: the identity of the composition
+      if (lane < nt) {
+        const float ir = DT<T>::to_f(reinterpret_cast<const T *>(p.iraw)[(m0 + lane) * p.ldg + h]) + ib;
+        const float fr = DT<T>::to_f(reinterpret_cast<const T *>(p.fraw)[(m0 + lane) * p.ldg + h]) + fb;
+        li = p.cap * tanhf(ir / p.cap);
+        const float z = p.cap * tanhf(fr / p.cap);
+        lf = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));  // log sigmoid(z)
+      }
+      float F = lf, I = li;   // inclusive scan of (F, I) over the lanes
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float Fp = __shfl_up_sync(0xffffffffu, F, o), Ip = __shfl_up_sync(0xffffffffu, I, o);
+        if (lane >= o) {
+          I = fmaxf(F + Ip, I);
+          F = Fp + F;
+        }
+      }
+      const float mt = fmaxf(F + mx, I);
+      float mp = __shfl_up_sync(0xffffffffu, mt, 1);
+      if (lane == 0) mp = mx;
+      if (lane < nt) {
+        as[lane] = expf(lf + mp - mt);
+        bs[lane] = expf(li - mt);
+        es[lane] = expf(-mt);
+      }
+      mx = __shfl_sync(0xffffffffu, mt, nt - 1);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      for (int tt = 0; tt < nt; tt++) {
+        const float a = as[tt], bb = bs[tt];
+        float dot = 0.f;
+        for (int r = lane; r < dk; r += 32) {
+          const float nv = fmaf(a, ns[r], bb * ks[tt * dk + r]);
+          ns[r] = nv;
+          dot = fmaf(nv, qs[tt * dk + r], dot);
+        }
+        dot = warp_sum(dot) * p.qscale;
+        if (lane == 0) {
+          const size_t o = (m0 + tt) * p.heads + h;
+          p.a[o] = a;
+          p.b[o] = bb;
+          p.div[o] = (fmaxf(fabsf(dot), es[tt]) + 1e-6f) / p.qscale;
+        }
+      }
     }
   }
-  __syncwarp();
-  for (int r = lane; r < dk; r += 32) aux[r] = ns[r];
-  if (lane == 0) aux[dk] = mx;
+  if (warp == 0) {
+    __syncwarp();
+    for (int r = lane; r < dk; r += 32) aux[r] = ns[r];
+    if (lane == 0) aux[dk] = mx;
+  }
 }
 int gate_prep(cudaStream_t st, int dtype, const GatePrep &p, uint64_t *launches) {
   if (p.B < 1 || p.S < 1 || p.heads < 1 || p.dk < 1 || !(p.cap > 0.f) || !(p.qscale > 0.f)) return (int)cudaErrorInvalidValue;
-  const size_t smem = ((size_t)p.dk * (1 + 2 * GP_TT) + 2 * GP_TT) * sizeof(float);
+  const size_t smem = ((size_t)p.dk * (1 + 2 * GP_TT) + 3 * GP_TT) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   MX_DISPATCH(dtype, {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(gate_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
     }
-    gate_prep_kernel<T><<<dim3(p.heads, p.B), 32, smem, st>>>(p);
+    gate_prep_kernel<T><<<dim3(p.heads, p.B), GP_THREADS, smem, st>>>(p);
   });
   MX_DONE(1);
 }
@@ -1735,6 +1816,127 @@ int talk_attention(cudaStream_t st, int dtype, const TalkAttn &p, uint64_t *laun
     }
   });
   MX_DONE(split ? 3 : 1);
+}
+
+// ---- the matrix-product form: softmax + head mixing between the two products
+// pass 1: a warp per (head, token) row: maximum and sum of exp over the keys the token sees
+__global__ void __launch_bounds__(256) talk_softmax_stats_kernel(const TalkSoftmax p) {
+  const long row = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= (long)p.heads * p.n_tok) return;
+  const int h = (int)(row / p.n_tok), t = (int)(row % p.n_tok), pos = p.pos_first + t;
+  const float *sr = p.scores + (size_t)row * p.kp;
+  float mx = -INFINITY, l = 0.f;
+  for (int j = lane; j <= pos; j += 32) {
+    const float s = fmaf(sr[j], p.scale, p.bias ? p.bias[(size_t)min(pos - j, p.bias_len - 1) * p.heads + h] : 0.f);
+    const float mn = fmaxf(mx, s);
+    l = l * expf(mx - mn) + expf(s - mn);
+    mx = mn;
+  }
+  const float m_all = warp_max(mx);
+  l = warp_sum(mx > -INFINITY ? l * expf(mx - m_all) : 0.f);
+  if (lane == 0) {
+    p.stats[2 * row] = m_all;
+    p.stats[2 * row + 1] = l;
+  }
+}
+// pass 2: a CTA per token: every thread normalises the scores of its keys for all heads, mixes them and stores hi | lo
+template <typename T>
+__global__ void __launch_bounds__(256) talk_softmax_mix_kernel(const TalkSoftmax p) {
+  extern __shared__ float sm[];
+  const int H = p.heads, NT = blockDim.x, t = blockIdx.x, pos = p.pos_first + t;
+  float *M_ = sm, *L_ = M_ + H, *tk = L_ + H, *pg = tk + H * H;   // pg[g * NT + tid]
+  for (int g = threadIdx.x; g < H; g += NT) {
+    M_[g] = p.stats[2 * ((size_t)g * p.n_tok + t)];
+    L_[g] = p.stats[2 * ((size_t)g * p.n_tok + t) + 1];
+  }
+  if (p.talk)
+    for (int i = threadIdx.x; i < H * H; i += NT) tk[i] = DT<T>::to_f(reinterpret_cast<const T *>(p.talk)[i]);
+  __syncthreads();
+  T *w = reinterpret_cast<T *>(p.w);
+  for (int j = threadIdx.x; j < p.kp; j += NT) {
+    const bool seen = j <= pos;
+    if (seen) {
+      const int dist = min(pos - j, p.bias_len - 1);
+      for (int g = 0; g < H; g++) {
+        const float s = fmaf(p.scores[((size_t)g * p.n_tok + t) * p.kp + j], p.scale, p.bias ? p.bias[(size_t)dist * H + g] : 0.f);
+        pg[g * NT + threadIdx.x] = expf(s - M_[g]) / L_[g];
+      }
+    }
+    for (int hh = 0; hh < H; hh++) {
+      float v = 0.f;
+      if (seen) {
+        if (p.talk)
+          for (int g = 0; g < H; g++) v = fmaf(tk[hh * H + g], pg[g * NT + threadIdx.x], v);
+        else v = pg[hh * NT + threadIdx.x];
+      }
+      const T hi = DT<T>::from_f(v);
+      T *wr = w + ((size_t)hh * p.n_tok + t) * 2 * p.kp;
+      wr[j] = hi;
+      wr[p.kp + j] = DT<T>::from_f(v - DT<T>::to_f(hi));
+    }
+  }
+}
+int talk_softmax(cudaStream_t st, int dtype, const TalkSoftmax &p, uint64_t *launches) {
+  if (p.n_tok < 1 || p.heads < 1 || p.kp < 1 || dtype == 2 || (p.bias && p.bias_len < 1)) return (int)cudaErrorInvalidValue;
+  const long rows = (long)p.heads * p.n_tok;
+  const size_t smem = ((size_t)2 * p.heads + (size_t)p.heads * p.heads + (size_t)p.heads * 256) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  talk_softmax_stats_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p);
+  MX_DISPATCH(dtype, {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(talk_softmax_mix_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    talk_softmax_mix_kernel<T><<<p.n_tok, 256, smem, st>>>(p);
+  });
+  MX_DONE(2);
+}
+template <typename T>
+__global__ void rows_by_head_kernel(const T *__restrict__ src, int ld, T *__restrict__ dst, int n_tok, int heads, int dim) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) dst[((size_t)(i / dim) * n_tok + t) * dim + i % dim] = src[(size_t)t * ld + i];
+}
+int rows_by_head(cudaStream_t st, int dtype, const void *src, int ld, void *dst, int n_tok, int heads, int dim, uint64_t *launches) {
+  MX_DISPATCH(dtype, (rows_by_head_kernel<T><<<n_tok, 256, 0, st>>>(reinterpret_cast<const T *>(src), ld, reinterpret_cast<T *>(dst), n_tok, heads, dim)));
+  MX_DONE(1);
+}
+template <typename T>
+__global__ void rows_to_tokens_kernel(const T *__restrict__ o, const T *__restrict__ gate, int ldg, T *__restrict__ out, int ldo, int n_tok, int heads, int vdim) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < heads * vdim; i += blockDim.x) {
+    float v = DT<T>::to_f(o[((size_t)(i / vdim) * n_tok + t) * vdim + i % vdim]);
+    if (gate) v *= 1.0f / (1.0f + expf(-DT<T>::to_f(gate[(size_t)t * ldg + i])));
+    out[(size_t)t * ldo + i] = DT<T>::from_f(v);
+  }
+}
+int rows_to_tokens(cudaStream_t st, int dtype, const void *o, const void *gate, int ldg, void *out, int ldo, int n_tok, int heads, int vdim,
+                   uint64_t *launches) {
+  MX_DISPATCH(dtype, (rows_to_tokens_kernel<T><<<n_tok, 256, 0, st>>>(reinterpret_cast<const T *>(o), reinterpret_cast<const T *>(gate), ldg,
+                                                                       reinterpret_cast<T *>(out), ldo, n_tok, heads, vdim)));
+  MX_DONE(1);
+}
+// a CTA transposes a tile of 32 tokens x 32 value entries through shared memory, so that reads and writes are both contiguous
+template <typename T>
+__global__ void values_transposed_kernel(const T *__restrict__ src, int ld, int col0, T *__restrict__ vt, int S, int kv_heads, int vdim, int cap_t, int pos0) {
+  __shared__ T tile[32][33];
+  const int b = blockIdx.z, t0 = blockIdx.x * 32, e0 = blockIdx.y * 32, n = kv_heads * vdim;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int t = t0 + r, e = e0 + threadIdx.x;
+    if (t < S && e < n) tile[r][threadIdx.x] = src[((size_t)b * S + t) * ld + col0 + e];
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int e = e0 + r, t = t0 + threadIdx.x;
+    if (t < S && e < n) vt[((size_t)b * n + e) * cap_t + pos0 + t] = tile[threadIdx.x][r];
+  }
+}
+int values_transposed_append(cudaStream_t st, int dtype, const void *src, int ld, int col0, void *vt, int B, int S, int kv_heads, int vdim, int cap_t,
+                             int pos0, uint64_t *launches) {
+  const dim3 grid((S + 31) / 32, (kv_heads * vdim + 31) / 32, B), block(32, 8);
+  MX_DISPATCH(dtype, (values_transposed_kernel<T><<<grid, block, 0, st>>>(reinterpret_cast<const T *>(src), ld, col0, reinterpret_cast<T *>(vt), S, kv_heads,
+                                                                          vdim, cap_t, pos0)));
+  MX_DONE(1);
 }
 
 template <typename T>

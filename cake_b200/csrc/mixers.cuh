@@ -278,6 +278,33 @@ struct TalkAttn {
   int nsplit = 0;
 };
 int talk_attention(cudaStream_t, int dtype, const TalkAttn &, uint64_t *launches);
+// The same attention as matrix products for long portions in 16-bit D.  Rows are (head, token) pairs of a block of n_tok tokens
+// of one batch row, row = head * n_tok + token, so that the rows of a key head's query heads are contiguous:
+//   rows_by_head   q [n_tok, ld] (heads * dim entries from column 0) -> [heads * n_tok, dim]
+//   (product)      scores [heads * n_tok, kp] fp32 = q rows . keys^T, per key head, kp = the visible keys padded to the tile
+//   talk_softmax   scale, distance bias, causal mask, softmax per row; then the heads' weights of a token are mixed and
+//                  leave as w_hi + w_lo in D, [heads * n_tok, 2 * kp]: hi in columns [0, kp), lo in [kp, 2 kp), zeros where
+//                  the token sees no key
+//   (product)      o [heads * n_tok, vdim] = [w_hi | w_lo] . values (the cache keeps the values once more, positions innermost)
+//   rows_to_tokens out[token, head * vdim + e] = o[head * n_tok + token, e] * sigmoid(gate[token, head * vdim + e])
+struct TalkSoftmax {
+  const float *scores;
+  void *w;
+  float *stats;          // [heads * n_tok, 2] scratch: row maximum and sum
+  const float *bias;     // as TalkAttn
+  int bias_len;
+  const void *talk;      // [heads, heads] D or nullptr
+  int n_tok, heads, kp, pos_first;   // pos_first: absolute position of the block's first token
+  float scale;
+};
+int talk_softmax(cudaStream_t, int dtype, const TalkSoftmax &, uint64_t *launches);
+int rows_by_head(cudaStream_t, int dtype, const void *src, int ld, void *dst, int n_tok, int heads, int dim, uint64_t *launches);
+int rows_to_tokens(cudaStream_t, int dtype, const void *o, const void *gate, int ldg, void *out, int ldo, int n_tok, int heads, int vdim,
+                   uint64_t *launches);
+// vt[b, g, e, pos0 + t] = src[(b, t), col0 + g * vdim + e]: the values of a step appended with the positions innermost
+int values_transposed_append(cudaStream_t, int dtype, const void *src, int ld, int col0, void *vt, int B, int S, int kv_heads, int vdim, int cap_t,
+                             int pos0, uint64_t *launches);
+
 // bias[d, h] = rel[bucket[d], h] for d < len (bucket: device ints): the per-distance form TalkAttn reads
 int distance_bias_table(cudaStream_t, int dtype, const void *rel, const int *bucket, float *bias, int len, int heads, uint64_t *launches);
 

@@ -420,6 +420,40 @@ def test_other_sizes_bf16_and_tensor_core_shapes():
 
 
 @pytest.mark.gpu
+def test_long_portions_on_the_tensor_cores():
+    """Sizes at which long portions in bf16 take the matrix-product form of the attention (several blocks of rows per key head,
+    with and without keys from earlier portions), against the plain model and against the same positions through the per-row
+    kernels; two batch rows through the same path."""
+    layers = [pair(heads=8, kv_heads=2, dim=64, vdim=128, scale=0.35, rows=14, bias_max=200, mheads=2, mdim=32, mvdim=64, ff=64, limit=3.0),
+              delta(heads=2, kv_heads=2, dim=32, vdim=64, conv=4, ff=0),
+              pair(heads=4, kv_heads=4, dim=128, vdim=128, scale=0.2, rows=6, bias_max=50, mheads=1, mdim=64, mvdim=32, ff=64, limit=1.0)]
+    cfg = make_config(layers, width=128, vocab=96, positions=1024)
+    sd = make_nuvarax_checkpoint(cfg, "bf16", seed=71)
+    toks = tokens(700, cfg.vocab_size, seed=13)
+    want = plain(cfg, sd, toks)
+    r = Runner(cfg, sd, "bf16")
+    try:
+        whole = r.run("w", toks)
+        close(whole, want, "bf16", "whole")
+        close(r.run("c", toks, cuts=[300, 390, 2, 1]), want, "bf16", "portions")
+        small = r.run("s", toks, cuts=[100])       # every portion below the matrix-product threshold
+        close(small, want, "bf16", "short portions")
+        assert np.quantile(errors(whole, small), 0.95) < TOL["bf16"]
+        from cake_b200.model import Cache
+        a, b = toks[:340], toks[340:680]
+        wa, wb = plain(cfg, sd, a), plain(cfg, sd, b)
+        r.ctx.cache = Cache(r.ctx, 2, cfg.max_seq_len)
+        g1 = r.model.forward(np.array([a[:200], b[:200]], dtype=np.uint32), 0, want=list(range(400)))
+        g2 = r.model.forward(np.array([a[200:], b[200:]], dtype=np.uint32), 200, want=list(range(280)))
+        r.ctx.sync()
+        g1, g2 = g1.cpu().numpy().reshape(2, 200, -1), g2.cpu().numpy().reshape(2, 140, -1)
+        close(np.concatenate([g1[0], g2[0]]), wa, "bf16", "batch row 0")
+        close(np.concatenate([g1[1], g2[1]]), wb, "bf16", "batch row 1")
+    finally:
+        r.close()
+
+
+@pytest.mark.gpu
 def test_greedy_generation_through_master():
     from cake_b200.model import Context, Master, TextModelBase
     cfg = full_config()
