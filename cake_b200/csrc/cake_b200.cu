@@ -155,6 +155,10 @@ struct cake_b200_ctx {
   void *bigram = nullptr, *pos_tab = nullptr;
   int bigram_rows = 0, mul_prev = 0, mul_cur = 0, pos_rows = 0;
   float final_norm_offset = 0.f;
+  // ext blocks with a side mixer: a recurrent side mixer runs on its own stream next to the main mixer (fork after the input
+  // projection, join before its output projection); created on first use
+  cudaStream_t side_stream = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   // comm
   ncclComm_t comm = nullptr;
   int rank = 0, world = 1;
@@ -582,6 +586,9 @@ extern "C" void cake_b200_ctx_destroy(cake_b200_ctx *c) {
     if (c->stage_free[i]) cudaEventDestroy(c->stage_free[i]);
   }
   if (c->load_done) cudaEventDestroy(c->load_done);
+  if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+  if (c->ev_join) cudaEventDestroy(c->ev_join);
+  if (c->side_stream) { cudaStreamSynchronize(c->side_stream); cudaStreamDestroy(c->side_stream); }
   if (c->load_stream) { cudaStreamSynchronize(c->load_stream); cudaStreamDestroy(c->load_stream); }
   if (c->h_pin) cudaFreeHost(c->h_pin);
   if (c->h_pin_x) cudaFreeHost(c->h_pin_x);
@@ -2102,10 +2109,9 @@ template <> int gemm_bias_tc<float>(cake_b200_ctx *, const void *, const void *,
 // one mixer of an ext block: proj [M, ldp] holds its projections at b->pc[]; y [M, hidden] fp32 receives o(att) without o's bias
 template <typename T>
 static int run_sub_mixer(cake_b200_ctx *c, const cake_b200_block *b, cake_b200_cache *kc, int slot, const SubScratch &w, const T *proj, int ldp,
-                         int B, int S, int pos0, uint64_t *lc) {
+                         int B, int S, int pos0, uint64_t *lc, cudaStream_t st, bool with_out) {
   const cake_b200_mixer_spec &sp = b->ms;
   const int M = B * S, H = c->cfg.hidden, dt = c->cfg.dtype, G = sp.kv_heads, inner = sp.heads * sp.vdim;
-  cudaStream_t st = c->stream;
   if (sp.kind == CAKE_B200_MIX_DELTA) {
     const int qk = G * sp.dim, ch = 2 * qk + inner;
     const T *cv = (const T *)w.conv;
@@ -2166,7 +2172,7 @@ static int run_sub_mixer(cake_b200_ctx *c, const cake_b200_block *b, cake_b200_c
     mx::GateNorm gn{w.o32, proj + b->pc[3], ldp, b->m_norm, w.att, M, inner, sp.heads, 0, c->cfg.rms_eps, 1, 0, w.f3};
     MX(mx::gate_norm(st, dt, gn, lc));
   }
-  return gemm_f32_out<T>(c, w.att, b->wo, w.y, M, H, inner);
+  return with_out ? gemm_f32_out<T>(c, w.att, b->wo, w.y, M, H, inner) : CAKE_B200_OK;
 }
 
 // one ext block: x_out = x + post1(mixers(canon(norm1(x)))), then x_out += post2(ff(norm2(x_out)))
@@ -2191,8 +2197,24 @@ static int enqueue_ext_layer(cake_b200_ctx *c, const cake_b200_block *b, int l, 
     RC((gemm_rows_T<T, RE_STORE>(c, gi)));
   }
   // 2. the mixer(s), each up to its output projection in fp32
-  RC(run_sub_mixer<T>(c, b, kc, l, w.a, (const T *)w.proj, b->n_in_pad, B, S, pos0, lc));
-  if (b->side) RC(run_sub_mixer<T>(c, b->side, kc, nl + l, w.b, (const T *)w.proj, b->n_in_pad, B, S, pos0, lc));
+  // a recurrent side mixer (its kernels take a stream; its few CTAs leave most of the chip idle) runs next to the main mixer
+  const bool fork = b->side && b->side->ms.kind != CAKE_B200_MIX_TALKING_ATTENTION && M >= 256 && !c->capturing;
+  if (fork) {
+    if (!c->side_stream) {
+      CU(cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking));
+      CU(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+      CU(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
+    }
+    CU(cudaEventRecord(c->ev_fork, st));
+    CU(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
+    RC(run_sub_mixer<T>(c, b->side, kc, nl + l, w.b, (const T *)w.proj, b->n_in_pad, B, S, pos0, lc, c->side_stream, false));
+    CU(cudaEventRecord(c->ev_join, c->side_stream));
+  }
+  RC(run_sub_mixer<T>(c, b, kc, l, w.a, (const T *)w.proj, b->n_in_pad, B, S, pos0, lc, st, true));
+  if (fork) {
+    CU(cudaStreamWaitEvent(st, c->ev_join, 0));
+    RC(gemm_f32_out<T>(c, w.b.att, b->side->wo, w.b.y, M, H, b->side->ms.heads * b->side->ms.vdim));
+  } else if (b->side) RC(run_sub_mixer<T>(c, b->side, kc, nl + l, w.b, (const T *)w.proj, b->n_in_pad, B, S, pos0, lc, st, true));
   // 3. x <- x + post1(branches)
   mx::BranchMerge bm{w.a.y, b->side ? w.b.y : nullptr, b->m_ob, b->side ? b->side->m_ob : nullptr, b->m_branch, b->side ? b->side->m_branch : nullptr,
                      b->post1, sp.norm_offset, cur, x_out, M, H, eps};

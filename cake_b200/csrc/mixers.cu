@@ -1348,7 +1348,9 @@ constexpr int DR_TT = 16, DR_CB = 32;
 template <typename T, int R, int RS>
 __global__ void __launch_bounds__(DR_CB * RS) delta_rule_kernel(const DeltaRule p) {
   extern __shared__ float sm[];
-  constexpr int ld = R * RS, NTH = DR_CB * RS;
+  // a lane's slice of a staged q / k row starts R + 4 floats after its neighbour's: the eight 16-byte reads of a quarter-warp
+  // then fall into different banks
+  constexpr int RP = RS > 1 ? R + 4 : R, ld = RP * RS, NTH = DR_CB * RS;
   float *qs = sm, *ks = qs + DR_TT * ld, *vs = ks + DR_TT * ld, *gs = vs + DR_TT * DR_CB, *bs = gs + DR_TT;
   const int dk = p.dk, dv = p.dv;
   const int ncb = (dv + DR_CB - 1) / DR_CB, h = blockIdx.x / ncb, cb = blockIdx.x % ncb, b = blockIdx.y;
@@ -1363,10 +1365,10 @@ __global__ void __launch_bounds__(DR_CB * RS) delta_rule_kernel(const DeltaRule 
     const int nt = min(DR_TT, p.S - t0);
     const size_t m0 = (size_t)b * p.S + t0;
     __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * ld; idx += NTH) {
-      const int tt = idx / ld, r = idx % ld;
-      qs[idx] = r < dk ? p.qn[(m0 + tt) * qk_ld + (size_t)kvh * dk + r] : 0.f;
-      ks[idx] = r < dk ? p.kn[(m0 + tt) * qk_ld + (size_t)kvh * dk + r] : 0.f;
+    for (int idx = threadIdx.x; idx < nt * R * RS; idx += NTH) {
+      const int tt = idx / (R * RS), r = idx % (R * RS), at = tt * ld + (r / R) * RP + r % R;
+      qs[at] = r < dk ? p.qn[(m0 + tt) * qk_ld + (size_t)kvh * dk + r] : 0.f;
+      ks[at] = r < dk ? p.kn[(m0 + tt) * qk_ld + (size_t)kvh * dk + r] : 0.f;
     }
     for (int idx = threadIdx.x; idx < nt * DR_CB; idx += NTH) {
       const int tt = idx / DR_CB, j = cb * DR_CB + idx % DR_CB;
@@ -1379,7 +1381,7 @@ __global__ void __launch_bounds__(DR_CB * RS) delta_rule_kernel(const DeltaRule 
     __syncthreads();
     for (int tt = 0; tt < nt; tt++) {
       const float g = gs[tt];
-      const float *kq = ks + tt * ld + s * R, *qq = qs + tt * ld + s * R;
+      const float *kq = ks + tt * ld + s * RP, *qq = qs + tt * ld + s * RP;
       float kr[R];
       float d0 = 0.f, d1 = 0.f;
 #pragma unroll
@@ -1469,7 +1471,7 @@ __global__ void __launch_bounds__(DR_CB) delta_rule_smem_kernel(const DeltaRule 
     for (int r = 0; r < dk; r++) gstate[(size_t)r * dv] = Ss[r * DR_CB + threadIdx.x];
 }
 template <typename T, int R, int RS> static cudaError_t launch_delta_rule(cudaStream_t st, const DeltaRule &p) {
-  const size_t smem = ((size_t)2 * DR_TT * R * RS + (size_t)DR_TT * DR_CB + 2 * DR_TT) * sizeof(float);
+  const size_t smem = ((size_t)2 * DR_TT * (RS > 1 ? R + 4 : R) * RS + (size_t)DR_TT * DR_CB + 2 * DR_TT) * sizeof(float);
   delta_rule_kernel<T, R, RS><<<dim3(p.heads * ((p.dv + DR_CB - 1) / DR_CB), p.B), DR_CB * RS, smem, st>>>(p);
   return cudaSuccess;
 }
@@ -1503,12 +1505,12 @@ int delta_rule(cudaStream_t st, int dtype, const DeltaRule &p, uint64_t *launche
 // One CTA of four warps per (head, batch row) walks the tokens in chunks of 32.  All threads stage the chunk's q and k; warp 0
 // computes the chunk's log gates (a lane per token), then the running maximum as a prefix scan: m' = max(f + m, i) composes as
 // (f1, i1) then (f2, i2) = (f1 + f2, max(f2 + i1, i2)); then it walks the tokens: lane l owns the entries l, l + 32, ... of n.
-constexpr int GP_TT = 32, GP_THREADS = 128;
+constexpr int GP_TT = 32, GP_THREADS = 128, GP_NE = 8;
 template <typename T>
 __global__ void __launch_bounds__(GP_THREADS) gate_prep_kernel(const GatePrep p) {
   extern __shared__ float sm[];
   const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, dk = p.dk;
-  float *ns = sm, *ks = ns + dk, *qs = ks + GP_TT * dk, *as = qs + GP_TT * dk, *bs = as + GP_TT, *es = bs + GP_TT;
+  float *ns = sm, *ks = ns + dk, *qs = ks + GP_TT * dk, *as = qs + GP_TT * dk, *bs = as + GP_TT, *es = bs + GP_TT, *dots = es + GP_TT;
   float *aux = p.aux + ((size_t)b * p.heads + h) * (dk + 1);
   if (warp == 0)
     for (int r = lane; r < dk; r += 32) ns[r] = p.pos0 > 0 ? aux[r] : 0.f;
@@ -1522,15 +1524,28 @@ __global__ void __launch_bounds__(GP_THREADS) gate_prep_kernel(const GatePrep p)
     if (vec) {
       typedef typename Bits16<T>::type B;
       const int c8 = dk / 8;
-      for (int idx = threadIdx.x; idx < nt * c8; idx += GP_THREADS) {
-        const int tt = idx / c8, r = (idx % c8) * 8;
-        float f[8];
-        unpack8<B>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.k) + (m0 + tt) * p.ld + (size_t)h * dk + r), f);
+      for (int base = threadIdx.x; base < nt * c8; base += 4 * GP_THREADS) {  // eight 16-byte loads in flight per thread
+        uint4 rk[4], rq[4];
 #pragma unroll
-        for (int e = 0; e < 8; e++) ks[tt * dk + r + e] = f[e];
-        unpack8<B>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.q) + (m0 + tt) * p.ld + (size_t)h * dk + r), f);
+        for (int u = 0; u < 4; u++) {
+          const int idx = min(base + u * GP_THREADS, nt * c8 - 1), tt = idx / c8, r = (idx % c8) * 8;
+          rk[u] = *reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.k) + (m0 + tt) * p.ld + (size_t)h * dk + r);
+          rq[u] = *reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.q) + (m0 + tt) * p.ld + (size_t)h * dk + r);
+        }
 #pragma unroll
-        for (int e = 0; e < 8; e++) qs[tt * dk + r + e] = f[e];
+        for (int u = 0; u < 4; u++) {
+          const int idx = base + u * GP_THREADS;
+          if (idx < nt * c8) {
+            const int tt = idx / c8, r = (idx % c8) * 8;
+            float f[8];
+            unpack8<B>(rk[u], f);
+#pragma unroll
+            for (int e = 0; e < 8; e++) ks[tt * dk + r + e] = f[e];
+            unpack8<B>(rq[u], f);
+#pragma unroll
+            for (int e = 0; e < 8; e++) qs[tt * dk + r + e] = f[e];
+          }
+        }
       }
     } else {
       for (int idx = threadIdx.x; idx < nt * dk; idx += GP_THREADS) {
@@ -1569,21 +1584,43 @@ __global__ void __launch_bounds__(GP_THREADS) gate_prep_kernel(const GatePrep p)
     }
     __syncthreads();
     if (warp == 0) {
+      const bool in_regs = dk <= 32 * GP_NE;   // the lane's entries of n stay in registers over the chunk
+      float nr[GP_NE];
+#pragma unroll
+      for (int e = 0; e < GP_NE; e++) nr[e] = (in_regs && lane + 32 * e < dk) ? ns[lane + 32 * e] : 0.f;
       for (int tt = 0; tt < nt; tt++) {
         const float a = as[tt], bb = bs[tt];
         float dot = 0.f;
-        for (int r = lane; r < dk; r += 32) {
-          const float nv = fmaf(a, ns[r], bb * ks[tt * dk + r]);
-          ns[r] = nv;
-          dot = fmaf(nv, qs[tt * dk + r], dot);
+        if (in_regs) {
+#pragma unroll
+          for (int e = 0; e < GP_NE; e++) {
+            const int r = min(lane + 32 * e, dk - 1);
+            nr[e] = fmaf(a, nr[e], bb * ks[tt * dk + r]);
+            dot = fmaf(lane + 32 * e < dk ? nr[e] : 0.f, qs[tt * dk + r], dot);
+          }
+        } else {
+          for (int r = lane; r < dk; r += 32) {
+            const float nv = fmaf(a, ns[r], bb * ks[tt * dk + r]);
+            ns[r] = nv;
+            dot = fmaf(nv, qs[tt * dk + r], dot);
+          }
         }
-        dot = warp_sum(dot) * p.qscale;
-        if (lane == 0) {
-          const size_t o = (m0 + tt) * p.heads + h;
-          p.a[o] = a;
-          p.b[o] = bb;
-          p.div[o] = (fmaxf(fabsf(dot), es[tt]) + 1e-6f) / p.qscale;
-        }
+        dots[tt * 32 + lane] = dot;   // the lanes' parts of n . q: added up after the walk, off its critical path
+      }
+      if (in_regs) {
+#pragma unroll
+        for (int e = 0; e < GP_NE; e++)
+          if (lane + 32 * e < dk) ns[lane + 32 * e] = nr[e];
+      }
+    }
+    __syncthreads();
+    for (int tt = warp; tt < nt; tt += GP_THREADS / 32) {
+      const float dot = warp_sum(dots[tt * 32 + lane]) * p.qscale;
+      if (lane == 0) {
+        const size_t o = (m0 + tt) * p.heads + h;
+        p.a[o] = as[tt];
+        p.b[o] = bs[tt];
+        p.div[o] = (fmaxf(fabsf(dot), es[tt]) + 1e-6f) / p.qscale;
       }
     }
   }
@@ -1595,7 +1632,7 @@ __global__ void __launch_bounds__(GP_THREADS) gate_prep_kernel(const GatePrep p)
 }
 int gate_prep(cudaStream_t st, int dtype, const GatePrep &p, uint64_t *launches) {
   if (p.B < 1 || p.S < 1 || p.heads < 1 || p.dk < 1 || !(p.cap > 0.f) || !(p.qscale > 0.f)) return (int)cudaErrorInvalidValue;
-  const size_t smem = ((size_t)p.dk * (1 + 2 * GP_TT) + 3 * GP_TT) * sizeof(float);
+  const size_t smem = ((size_t)p.dk * (1 + 2 * GP_TT) + 3 * GP_TT + 32 * GP_TT) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   MX_DISPATCH(dtype, {
     if (smem > 48 * 1024) {
@@ -1840,6 +1877,73 @@ __global__ void __launch_bounds__(256) talk_softmax_stats_kernel(const TalkSoftm
     p.stats[2 * row + 1] = l;
   }
 }
+// pass 2 for up to HP heads: a CTA per token; a thread owns four adjacent keys: 16-byte reads of the scores, the normalised
+// weights of all heads in registers, a row of the mixing matrix (read from shared memory four entries at a time) serves the four
+// keys, and hi and lo leave as 8-byte stores
+template <typename T, int HP>
+__global__ void __launch_bounds__(256) talk_softmax_mix_regs_kernel(const TalkSoftmax p) {
+  __shared__ __align__(16) float tk[HP * HP];
+  __shared__ float M_[HP], L_[HP];
+  const int H = p.heads, NT = blockDim.x, t = blockIdx.x, pos = p.pos_first + t;
+  for (int i = threadIdx.x; i < HP * HP; i += NT) {
+    const int hh = i / HP, g = i % HP;
+    tk[i] = (hh < H && g < H) ? (p.talk ? DT<T>::to_f(reinterpret_cast<const T *>(p.talk)[hh * H + g]) : (hh == g ? 1.f : 0.f)) : 0.f;
+  }
+  for (int g = threadIdx.x; g < HP; g += NT) {
+    M_[g] = g < H ? p.stats[2 * ((size_t)g * p.n_tok + t)] : 0.f;
+    L_[g] = g < H ? 1.0f / p.stats[2 * ((size_t)g * p.n_tok + t) + 1] : 1.f;
+  }
+  __syncthreads();
+  T *w = reinterpret_cast<T *>(p.w);
+  for (int j0 = 4 * threadIdx.x; j0 < p.kp; j0 += 4 * NT) {
+    float pr[HP][4];
+    if (j0 > pos) {   // nothing of these four keys is seen: zeros
+#pragma unroll 4
+      for (int hh = 0; hh < H; hh++) {
+        T *wr = w + ((size_t)hh * p.n_tok + t) * 2 * p.kp;
+        *reinterpret_cast<uint2 *>(wr + j0) = make_uint2(0u, 0u);
+        *reinterpret_cast<uint2 *>(wr + p.kp + j0) = make_uint2(0u, 0u);
+      }
+      continue;
+    }
+#pragma unroll
+    for (int g = 0; g < HP; g++) {
+      pr[g][0] = pr[g][1] = pr[g][2] = pr[g][3] = 0.f;
+      if (g < H) {
+        const float4 s4 = *reinterpret_cast<const float4 *>(p.scores + ((size_t)g * p.n_tok + t) * p.kp + j0);
+        const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++)
+          if (j0 + e <= pos) {
+            const float sc = fmaf(sv[e], p.scale, p.bias ? p.bias[(size_t)min(pos - j0 - e, p.bias_len - 1) * H + g] : 0.f);
+            pr[g][e] = expf(sc - M_[g]) * L_[g];
+          }
+      }
+    }
+#pragma unroll 2
+    for (int hh = 0; hh < H; hh++) {
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int g = 0; g < HP; g += 4) {
+        const float4 t4 = *reinterpret_cast<const float4 *>(tk + hh * HP + g);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          v[e] = fmaf(t4.x, pr[g][e], v[e]);
+          v[e] = fmaf(t4.y, pr[g + 1][e], v[e]);
+          v[e] = fmaf(t4.z, pr[g + 2][e], v[e]);
+          v[e] = fmaf(t4.w, pr[g + 3][e], v[e]);
+        }
+      }
+      typedef typename Bits16<T>::type B;
+      float lo[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) lo[e] = v[e] - rnd<B>(v[e]);
+      T *wr = w + ((size_t)hh * p.n_tok + t) * 2 * p.kp;
+      *reinterpret_cast<uint2 *>(wr + j0) = make_uint2(pack2x<B>(v[0], v[1]), pack2x<B>(v[2], v[3]));
+      *reinterpret_cast<uint2 *>(wr + p.kp + j0) = make_uint2(pack2x<B>(lo[0], lo[1]), pack2x<B>(lo[2], lo[3]));
+    }
+  }
+}
 // pass 2: a CTA per token: every thread normalises the scores of its keys for all heads, mixes them and stores hi | lo
 template <typename T>
 __global__ void __launch_bounds__(256) talk_softmax_mix_kernel(const TalkSoftmax p) {
@@ -1884,11 +1988,17 @@ int talk_softmax(cudaStream_t st, int dtype, const TalkSoftmax &p, uint64_t *lau
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   talk_softmax_stats_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p);
   MX_DISPATCH(dtype, {
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(talk_softmax_mix_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
+    if (p.heads <= 4) talk_softmax_mix_regs_kernel<T, 4><<<p.n_tok, 256, 0, st>>>(p);
+    else if (p.heads <= 8) talk_softmax_mix_regs_kernel<T, 8><<<p.n_tok, 256, 0, st>>>(p);
+    else if (p.heads <= 16) talk_softmax_mix_regs_kernel<T, 16><<<p.n_tok, 256, 0, st>>>(p);
+    else if (p.heads <= 32) talk_softmax_mix_regs_kernel<T, 32><<<p.n_tok, 256, 0, st>>>(p);
+    else {
+      if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(talk_softmax_mix_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+      }
+      talk_softmax_mix_kernel<T><<<p.n_tok, 256, smem, st>>>(p);
     }
-    talk_softmax_mix_kernel<T><<<p.n_tok, 256, smem, st>>>(p);
   });
   MX_DONE(2);
 }
