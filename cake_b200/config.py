@@ -349,7 +349,7 @@ class Config:
             kind, m = L.get("type"), L["mixer"]
             if kind == "delta":
                 sp = MixerSpec(type="delta", heads=int(m["heads"]), kv_heads=int(m.get("kv_heads") or m["heads"]), dim=int(m["dim"]),
-                               vdim=int(m["vdim"]), conv=int(m.get("conv") or 1))
+                               vdim=int(m["vdim"]), conv=int(m.get("conv") or 0))   # 0: the taps are the convolution tensors' second size
             elif kind == "parallel":
                 a, b = m["left"], m["right"]
                 sp = MixerSpec(type="talking_attention", heads=int(a["heads"]), kv_heads=int(a.get("kv_heads") or a["heads"]), dim=int(a["dim"]),

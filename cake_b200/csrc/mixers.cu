@@ -1234,6 +1234,51 @@ __global__ void __launch_bounds__(256) canon_conv_kernel(const CanonConv p) {
     reinterpret_cast<T *>(p.out)[(size_t)m * p.n + ch] = DT<T>::from_f(acc);
   }
 }
+// widths that are multiples of four with up to eight taps: a thread owns four channels and walks CC_TOK tokens with a sliding
+// window of inputs in registers, so that a row of h is read once (16-byte loads) and the output leaves as 8- or 16-byte stores
+constexpr int CC_TOK = 16, CC_MAXT = 8;
+template <typename T>
+__global__ void __launch_bounds__(128) canon_conv_vec_kernel(const CanonConv p) {
+  const int c4 = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c4 >= p.n / 4) return;
+  const int ch = c4 * 4, chunks = (p.S + CC_TOK - 1) / CC_TOK, b = blockIdx.x / chunks, t0 = (blockIdx.x % chunks) * CC_TOK, back = p.taps - 1;
+  const T *w = reinterpret_cast<const T *>(p.w);
+  const float *h = p.h + (size_t)b * p.S * p.n + ch, *hist = p.hist + (size_t)b * back * p.n + ch;
+  float wt[4][CC_MAXT], x[CC_MAXT][4];
+#pragma unroll
+  for (int e = 0; e < 4; e++)
+#pragma unroll
+    for (int jt = 0; jt < CC_MAXT; jt++) wt[e][jt] = jt < p.taps ? DT<T>::to_f(w[(size_t)(ch + e) * p.taps + jt]) : 0.f;
+  // window slot CC_MAXT - 1 is the current token, slot CC_MAXT - 1 - d the token d back; slots further back than `back` stay zero
+#pragma unroll
+  for (int d = 1; d < CC_MAXT; d++) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (d <= back) {
+      const int tt = t0 - d;
+      if (tt >= 0) v = *reinterpret_cast<const float4 *>(h + (size_t)tt * p.n);
+      else if (p.pos0 > 0) v = *reinterpret_cast<const float4 *>(hist + (size_t)(back + tt) * p.n);
+    }
+    x[CC_MAXT - 1 - d][0] = v.x; x[CC_MAXT - 1 - d][1] = v.y; x[CC_MAXT - 1 - d][2] = v.z; x[CC_MAXT - 1 - d][3] = v.w;
+  }
+  const int t1 = min(p.S, t0 + CC_TOK);
+  for (int t = t0; t < t1; t++) {
+    const float4 v = *reinterpret_cast<const float4 *>(h + (size_t)t * p.n);
+    x[CC_MAXT - 1][0] = v.x; x[CC_MAXT - 1][1] = v.y; x[CC_MAXT - 1][2] = v.z; x[CC_MAXT - 1][3] = v.w;
+    float acc[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      acc[e] = x[CC_MAXT - 1][e];
+#pragma unroll
+      for (int d = 0; d < CC_MAXT; d++)   // tap index taps - 1 - d multiplies the token d back
+        if (d <= back) acc[e] = fmaf(wt[e][back - d], x[CC_MAXT - 1 - d][e], acc[e]);
+    }
+    store4<T>(reinterpret_cast<T *>(p.out) + ((size_t)b * p.S + t) * p.n + ch, acc);
+#pragma unroll
+    for (int d = CC_MAXT - 1; d >= 1; d--)
+#pragma unroll
+      for (int e = 0; e < 4; e++) x[CC_MAXT - 1 - d][e] = x[CC_MAXT - d][e];
+  }
+}
 // afterwards: the history becomes the last taps - 1 inputs up to the end of this step (zeros before position 0)
 __global__ void canon_hist_kernel(const CanonConv p) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x, back = p.taps - 1;
@@ -1250,7 +1295,11 @@ __global__ void canon_hist_kernel(const CanonConv p) {
 }
 int canon_conv(cudaStream_t st, int dtype, const CanonConv &p, uint64_t *launches) {
   if (p.taps < 1 || p.B < 1 || p.S < 1) return (int)cudaErrorInvalidValue;
-  MX_DISPATCH(dtype, (canon_conv_kernel<T><<<dim3(p.B * p.S, (p.n + 255) / 256), 256, 0, st>>>(p)));
+  const bool vec = p.n % 4 == 0 && p.taps <= CC_MAXT && (((uintptr_t)p.h | (uintptr_t)p.hist | (uintptr_t)p.out) & 15) == 0;
+  MX_DISPATCH(dtype, {
+    if (vec) canon_conv_vec_kernel<T><<<dim3(p.B * ((p.S + CC_TOK - 1) / CC_TOK), (p.n / 4 + 127) / 128), 128, 0, st>>>(p);
+    else canon_conv_kernel<T><<<dim3(p.B * p.S, (p.n + 255) / 256), 256, 0, st>>>(p);
+  });
   if (p.taps > 1) canon_hist_kernel<<<(p.B * p.n + 255) / 256, 256, 0, st>>>(p);
   MX_DONE(p.taps > 1 ? 2 : 1);
 }

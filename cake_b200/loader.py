@@ -361,6 +361,14 @@ def nuvarax_block_tensors(vb, cfg: Config, index: int):
             raise ValueError(f"shape mismatch for {name}.{short}, expected: {list(shape)}, got: {list(t.shape)}")
         return t
 
+    def taps_of(short):   # a size the config may leave to the tensor's shape
+        t = vb.get(f"{name}.{short}")
+        return int(t.shape[1]) if t is not None and t.dim() == 2 else 0
+
+    if not sp.canon_taps:
+        sp.canon_taps = taps_of("canon1")
+    if sp.type == "delta" and not sp.conv:
+        sp.conv = taps_of("mix.q.conv") or 1
     main = {"norm1": get("norm1", (H,))}
     if sp.post_norms:
         main["post1"] = get("norm1b", (H,))

@@ -151,6 +151,14 @@ def test_checkpoint_names_and_shapes():
     broken["l1.mix.q.conv"] = sd["l1.mix.q.conv"][:, :-1]
     with pytest.raises(ValueError):
         nuvarax_block_tensors(broken, cfg, 1)
+    # a config that leaves the taps to the tensors' shapes
+    d = cfg.to_hf()
+    d["canon"] = None
+    del d["layers"][1]["mixer"]["conv"]
+    bare = Config.from_hf(json.loads(json.dumps(d)))
+    assert bare.layers[1].conv == 0 and bare.layers[1].canon_taps == 0
+    main, _ = nuvarax_block_tensors(sd, bare, 1)
+    assert bare.layers[1].conv == 3 and bare.layers[1].canon_taps == 3 and main["canon"].shape == (cfg.hidden_size, 3)
 
 
 def test_plain_distance_buckets():
