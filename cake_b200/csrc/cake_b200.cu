@@ -2054,7 +2054,7 @@ template <typename Take> static SubScratch sub_scratch(const cake_b200_ctx *c, c
     }
     // steps of a few rows over many keys: split the keys so that the step fills the chip
     if (M <= 32 && n_keys >= 256) {
-      s.nsplit = (int)std::min<size_t>(TALK_SPLIT_MAX, std::min<size_t>((n_keys + 127) / 128, (2 * (size_t)c->sm_count + M - 1) / M));
+      s.nsplit = (int)std::min<size_t>(TALK_SPLIT_MAX, std::min<size_t>((n_keys + 63) / 64, (2 * (size_t)c->sm_count + M - 1) / M));
       if (s.nsplit > 1) s.part = (float *)take(M * s.nsplit * (2 * (size_t)sp.heads + inner) * sizeof(float));
       else s.nsplit = 0;
     }

@@ -1701,18 +1701,27 @@ __device__ __forceinline__ void key_scores8(const T *__restrict__ krow, const fl
   for (int i = 0; i < 8; i++) acc[i] = 0.f;
   if (sizeof(T) == 2 && (dim & 7) == 0 && ((uintptr_t)krow & 15) == 0) {
     typedef typename Bits16<T>::type B;
-    for (int d = 0; d < dim; d += 8) {
-      float kf[8];
-      unpack8<B>(*reinterpret_cast<const uint4 *>(krow + d), kf);
+    for (int d0 = 0; d0 < dim; d0 += 32) {   // four 16-byte loads of the key row in flight
+      uint4 kr[4];
 #pragma unroll
-      for (int i = 0; i < 8; i++)
-        if (i < ng) {
-          const float4 qa = *reinterpret_cast<const float4 *>(q + i * dim + d), qb = *reinterpret_cast<const float4 *>(q + i * dim + d + 4);
-          float s = acc[i];
-          s = fmaf(kf[0], qa.x, s); s = fmaf(kf[1], qa.y, s); s = fmaf(kf[2], qa.z, s); s = fmaf(kf[3], qa.w, s);
-          s = fmaf(kf[4], qb.x, s); s = fmaf(kf[5], qb.y, s); s = fmaf(kf[6], qb.z, s); s = fmaf(kf[7], qb.w, s);
-          acc[i] = s;
+      for (int u = 0; u < 4; u++) kr[u] = *reinterpret_cast<const uint4 *>(krow + min(d0 + 8 * u, dim - 8));
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int d = d0 + 8 * u;
+        if (d < dim) {
+          float kf[8];
+          unpack8<B>(kr[u], kf);
+#pragma unroll
+          for (int i = 0; i < 8; i++)
+            if (i < ng) {
+              const float4 qa = *reinterpret_cast<const float4 *>(q + i * dim + d), qb = *reinterpret_cast<const float4 *>(q + i * dim + d + 4);
+              float s = acc[i];
+              s = fmaf(kf[0], qa.x, s); s = fmaf(kf[1], qa.y, s); s = fmaf(kf[2], qa.z, s); s = fmaf(kf[3], qa.w, s);
+              s = fmaf(kf[4], qb.x, s); s = fmaf(kf[5], qb.y, s); s = fmaf(kf[6], qb.z, s); s = fmaf(kf[7], qb.w, s);
+              acc[i] = s;
+            }
         }
+      }
     }
     return;
   }
@@ -1724,9 +1733,12 @@ __device__ __forceinline__ void key_scores8(const T *__restrict__ krow, const fl
   }
 }
 
-// One CTA per query row (and per key range when the keys are split), all heads.  Pass 1: every thread keeps a running
-// (max, sum) per head over its keys, merged per head at the end.  Pass 2: the scores are computed again, normalised, mixed
-// across heads, and a tile of mixed weights in shared memory is applied to the values by threads that own output entries.
+// One CTA per query row (and per key range when the keys are split), all heads.  A thread works on one (key, key head) pair of a
+// tile of KT = blockDim / kv_heads keys: it computes the scores of that key head's query heads.  Pass 1: every thread keeps a
+// running (max, sum) per head over its keys, merged per head at the end.  Pass 2: the scores are computed again and normalised;
+// after a barrier the thread mixes the weights of its key for its key head's heads across all heads, and after another the tile
+// of mixed weights in shared memory is applied to the values by threads that own output entries (eight adjacent ones and
+// 16-byte value loads where the sizes allow).
 // PHASE 0: both passes in one kernel.  PHASE 1 / 2: the passes of the split form (stats of a key range -> part; the second
 // pass merges the ranges' stats itself and leaves partial outputs in part).
 constexpr int TA_MAXO = 16;
@@ -1744,27 +1756,13 @@ __global__ void __launch_bounds__(256) talk_attn_kernel(const TalkAttn p) {
   if (p.talk)
     for (int i = threadIdx.x; i < H * H; i += NT) tk[i] = DT<T>::to_f(reinterpret_cast<const T *>(p.talk)[i]);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = NT >> 5;
-  auto score_all = [&](int j, float *dst /* dst[g * NT + tid] */) {
-    const int dist = min(pos - j, p.bias_len - 1);
-    for (int c = 0; c < G; c++) {
-      const T *krow = kc + ((size_t)c * p.cap + j) * dim;
-      for (int g0 = 0; g0 < grp; g0 += 8) {
-        const int ng = min(8, grp - g0), gb = c * grp + g0;
-        float acc[8];
-        key_scores8<T>(krow, qs + (size_t)gb * dim, ng, dim, acc);
-#pragma unroll
-        for (int i = 0; i < 8; i++)
-          if (i < ng) dst[(size_t)(gb + i) * NT + threadIdx.x] = fmaf(acc[i], p.scale, p.bias ? p.bias[(size_t)dist * H + gb + i] : 0.f);
-      }
-    }
-  };
+  const int KT = NT / G, kl = threadIdx.x % KT, c = threadIdx.x / KT;   // this thread's key slot and key head (c >= G: idle)
   if (PHASE != 2) {
     for (int g = 0; g < H; g++) { ta[(size_t)g * NT + threadIdx.x] = -INFINITY; tb[(size_t)g * NT + threadIdx.x] = 0.f; }
-    __syncthreads();  // qs
-    // running (max, sum) per head of this thread's keys; the fresh scores pass through the first H entries of sc
-    for (int j = k_lo + threadIdx.x; j < k_hi; j += NT) {
-      const int dist = min(pos - j, p.bias_len - 1);
-      for (int c = 0; c < G; c++) {
+    __syncthreads();  // qs, and the initial stats
+    if (c < G)
+      for (int j = k_lo + kl; j < k_hi; j += KT) {
+        const int dist = min(pos - j, p.bias_len - 1);
         const T *krow = kc + ((size_t)c * p.cap + j) * dim;
         for (int g0 = 0; g0 < grp; g0 += 8) {
           const int ng = min(8, grp - g0), gb = c * grp + g0;
@@ -1774,21 +1772,20 @@ __global__ void __launch_bounds__(256) talk_attn_kernel(const TalkAttn p) {
           for (int i = 0; i < 8; i++)
             if (i < ng) {
               const float s = fmaf(acc[i], p.scale, p.bias ? p.bias[(size_t)dist * H + gb + i] : 0.f);
-              const size_t o = (size_t)(gb + i) * NT + threadIdx.x;
+              const size_t o = (size_t)(gb + i) * NT + kl;   // slot kl of head gb + i: only this thread touches it
               const float mo = ta[o], mn = fmaxf(mo, s);
               tb[o] = tb[o] * expf(mo - mn) + expf(s - mn);  // exp(-inf) = 0 on the first key
               ta[o] = mn;
             }
         }
       }
-    }
     __syncthreads();
-    for (int g = warp; g < H; g += nw) {  // merge the threads' pairs of head g
+    for (int g = warp; g < H; g += nw) {  // merge the slots of head g
       float mx = -INFINITY;
-      for (int i = lane; i < NT; i += 32) mx = fmaxf(mx, ta[(size_t)g * NT + i]);
+      for (int i = lane; i < KT; i += 32) mx = fmaxf(mx, ta[(size_t)g * NT + i]);
       mx = warp_max(mx);
       float l = 0.f;
-      for (int i = lane; i < NT; i += 32) {
+      for (int i = lane; i < KT; i += 32) {
         const float mi = ta[(size_t)g * NT + i];
         if (mi > -INFINITY) l += tb[(size_t)g * NT + i] * expf(mi - mx);
       }
@@ -1819,51 +1816,90 @@ __global__ void __launch_bounds__(256) talk_attn_kernel(const TalkAttn p) {
   }
   // pass 2, once per TA_MAXO * NT output entries (one round unless heads * vdim exceeds that)
   const int n_out = H * vdim;
-  for (int o0 = 0; o0 < n_out; o0 += TA_MAXO * NT) {
-  float acc[TA_MAXO];
+  const bool vec = sizeof(T) == 2 && (vdim & 7) == 0 && (((uintptr_t)p.vc) & 15) == 0;   // eight adjacent entries per work item
+  const int n_items = vec ? n_out / 8 : n_out, per_round = vec ? (TA_MAXO / 8) * NT : TA_MAXO * NT;
+  for (int o0 = 0; o0 < n_items; o0 += per_round) {
+    float acc[TA_MAXO];
 #pragma unroll
-  for (int k = 0; k < TA_MAXO; k++) acc[k] = 0.f;
-  for (int j0 = k_lo; j0 < k_hi; j0 += NT) {
-    const int j = j0 + threadIdx.x, nj = min(NT, k_hi - j0);
-    if (j < k_hi) {
-      score_all(j, ta);
-      for (int g = 0; g < H; g++) ta[(size_t)g * NT + threadIdx.x] = expf(ta[(size_t)g * NT + threadIdx.x] - M_[g]) / L_[g];
-      if (p.talk)
-        for (int hh = 0; hh < H; hh++) {
-          float w = 0.f;
-          for (int g = 0; g < H; g++) w = fmaf(tk[hh * H + g], ta[(size_t)g * NT + threadIdx.x], w);
-          tb[(size_t)hh * NT + threadIdx.x] = w;
+    for (int k = 0; k < TA_MAXO; k++) acc[k] = 0.f;
+    for (int j0 = k_lo; j0 < k_hi; j0 += KT) {
+      const int j = j0 + kl, nj = min(KT, k_hi - j0);
+      const bool mine = c < G && j < k_hi;
+      if (mine) {
+        const int dist = min(pos - j, p.bias_len - 1);
+        const T *krow = kc + ((size_t)c * p.cap + j) * dim;
+        for (int g0 = 0; g0 < grp; g0 += 8) {
+          const int ng = min(8, grp - g0), gb = c * grp + g0;
+          float sc[8];
+          key_scores8<T>(krow, qs + (size_t)gb * dim, ng, dim, sc);
+#pragma unroll
+          for (int i = 0; i < 8; i++)
+            if (i < ng) {
+              const float s = fmaf(sc[i], p.scale, p.bias ? p.bias[(size_t)dist * H + gb + i] : 0.f);
+              ta[(size_t)(gb + i) * NT + kl] = expf(s - M_[gb + i]) / L_[gb + i];
+            }
         }
+      }
+      if (p.talk) {
+        __syncthreads();   // the weights of every head for this tile's keys
+        if (mine)
+          for (int hh = c * grp; hh < (c + 1) * grp; hh++) {
+            float wv = 0.f;
+            for (int g = 0; g < H; g++) wv = fmaf(tk[hh * H + g], ta[(size_t)g * NT + kl], wv);
+            tb[(size_t)hh * NT + kl] = wv;
+          }
+      }
+      __syncthreads();
+      const float *wt = p.talk ? tb : ta;
+      if (vec) {
+        typedef typename Bits16<T>::type B;
+#pragma unroll
+        for (int k = 0; k < TA_MAXO / 8; k++) {
+          const int it = o0 + threadIdx.x + k * NT;
+          if (it < n_items) {
+            const int hh = (it * 8) / vdim, e = (it * 8) % vdim;
+            const T *vcol = vc + ((size_t)(hh / grp) * p.cap + j0) * vdim + e;
+            const float *wrow = wt + (size_t)hh * NT;
+            for (int jj = 0; jj < nj; jj++) {
+              float vf[8];
+              unpack8<B>(*reinterpret_cast<const uint4 *>(vcol + (size_t)jj * vdim), vf);
+              const float wj = wrow[jj];
+#pragma unroll
+              for (int x = 0; x < 8; x++) acc[8 * k + x] = fmaf(wj, vf[x], acc[8 * k + x]);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < TA_MAXO; k++) {
+          const int idx = o0 + threadIdx.x + k * NT;
+          if (idx < n_out) {
+            const int hh = idx / vdim, e = idx % vdim;
+            const T *vcol = vc + ((size_t)(hh / grp) * p.cap + j0) * vdim + e;
+            const float *wrow = wt + (size_t)hh * NT;
+            float a = acc[k];
+            for (int jj = 0; jj < nj; jj++) a = fmaf(wrow[jj], DT<T>::to_f(vcol[(size_t)jj * vdim]), a);
+            acc[k] = a;
+          }
+        }
+      }
+      __syncthreads();
     }
-    __syncthreads();
-    const float *wt = p.talk ? tb : ta;
 #pragma unroll
     for (int k = 0; k < TA_MAXO; k++) {
-      const int idx = o0 + threadIdx.x + k * NT;
-      if (idx < n_out) {
-        const int hh = idx / vdim, e = idx % vdim;
-        const T *vcol = vc + ((size_t)(hh / grp) * p.cap + j0) * vdim + e;
-        const float *wrow = wt + (size_t)hh * NT;
-        float a = acc[k];
-        for (int jj = 0; jj < nj; jj++) a = fmaf(wrow[jj], DT<T>::to_f(vcol[(size_t)jj * vdim]), a);
-        acc[k] = a;
+      // the output entry of accumulator k: eight adjacent ones per work item in the vector form
+      const int idx = vec ? (o0 + threadIdx.x + (k / 8) * NT) * 8 + k % 8 : o0 + threadIdx.x + k * NT;
+      const bool live = vec ? (o0 + threadIdx.x + (k / 8) * NT) < n_items : idx < n_out;
+      if (live) {
+        if (PHASE == 2) {
+          p.part[(size_t)p.B * p.S * ns * H * 2 + ((size_t)m * ns + sp) * n_out + idx] = acc[k];
+        } else {
+          float o = acc[k];
+          if (p.gate) o *= 1.0f / (1.0f + expf(-DT<T>::to_f(reinterpret_cast<const T *>(p.gate)[(size_t)m * p.ldg + idx])));
+          reinterpret_cast<T *>(p.out)[(size_t)m * n_out + idx] = DT<T>::from_f(o);
+        }
       }
     }
-    __syncthreads();
-  }
-#pragma unroll
-  for (int k = 0; k < TA_MAXO; k++) {
-    const int idx = o0 + threadIdx.x + k * NT;
-    if (idx < n_out) {
-      if (PHASE == 2) {
-        p.part[(size_t)p.B * p.S * ns * H * 2 + ((size_t)m * ns + sp) * n_out + idx] = acc[k];
-      } else {
-        float o = acc[k];
-        if (p.gate) o *= 1.0f / (1.0f + expf(-DT<T>::to_f(reinterpret_cast<const T *>(p.gate)[(size_t)m * p.ldg + idx])));
-        reinterpret_cast<T *>(p.out)[(size_t)m * n_out + idx] = DT<T>::from_f(o);
-      }
-    }
-  }
   }
 }
 // the split form's last step: the key ranges' partial outputs are added in range order, gated and stored in D
@@ -1879,7 +1915,7 @@ __global__ void __launch_bounds__(256) talk_attn_merge_kernel(const TalkAttn p) 
   }
 }
 int talk_attention(cudaStream_t st, int dtype, const TalkAttn &p, uint64_t *launches) {
-  if (p.B < 1 || p.S < 1 || p.heads < 1 || p.kv_heads < 1 || p.heads % p.kv_heads || p.dim < 1 || p.vdim < 1 || (p.bias && p.bias_len < 1))
+  if (p.B < 1 || p.S < 1 || p.heads < 1 || p.kv_heads < 1 || p.heads % p.kv_heads || p.dim < 1 || p.vdim < 1 || (p.bias && p.bias_len < 1) || p.kv_heads > 64)
     return (int)cudaErrorInvalidValue;
   const int NT = 256;
   const size_t smem = ((size_t)p.heads * p.dim + 2 * p.heads + (size_t)p.heads * p.heads + 2 * (size_t)p.heads * NT) * sizeof(float);
