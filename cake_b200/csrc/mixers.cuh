@@ -1,7 +1,9 @@
 // mixers.cuh — launch interface of the sequence mixers and the routed feed-forward of mixer-list blocks
 // (cake_b200_block_load_mixer): latent attention (keys and values expanded from a cached low-rank latent), gated linear
-// recurrences (a fixed decay per head, or input-dependent decays of a state-space layer), short causal convolutions,
-// grouped unit norms with gates, and a mixture of experts with identity experts.  The kernels live in mixers.cu, a
+// recurrences (a fixed decay per head, input-dependent decays of a state-space layer, or per-token factors of a matrix memory
+// with exponential gates), the gated delta rule, softmax attention whose heads are mixed after the softmax, short causal
+// convolutions, grouped unit norms with gates, norms and merges of sublayer outputs on the fp32 stream, embeddings with pair and
+// position tables, and a mixture of experts with identity experts.  The kernels live in mixers.cu, a
 // translation unit of its own; the entry points below take plain device pointers and a stream, so that any block
 // structure can combine them.  Every function returns a cudaError_t cast to int and adds its launches to *launches.
 //

@@ -168,7 +168,8 @@ int cake_b200_block_load_spec(cake_b200_ctx *, int layer_idx, const cake_b200_la
 /* ---- mixer-list blocks ----------------------------------------------------------------------------
  * One layer of a model with cake_b200_config.layer_list whose block is SEQUENTIAL and pre-normed,
  *     x <- x + mixer(norm1(x));   x <- x + ff(norm2(x))          (RMS norms with [hidden] gains, fp32)
- * with one of three sequence mixers and an optional routed feed-forward.  Every size and constant is a parameter; a
+ * with one of the sequence mixers below and an optional routed feed-forward (the structure switches further down change the
+ * block: norms behind the sublayers, gains stored as offsets, an input convolution, a side mixer, a dense feed-forward).  Every size and constant is a parameter; a
  * combination that is not built is refused with CAKE_B200_EINVAL.  Scores, softmax, norms, rotations, recurrent state,
  * decays, the router and the residual sums are fp32; projections, caches and weights are in D.
  *   CAKE_B200_MIX_LATENT     attention whose keys and values are expanded from a cached low-rank latent: per head
