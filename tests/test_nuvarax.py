@@ -210,6 +210,9 @@ MECHANISMS = {
     "delta_key_size_80": lambda: make_config([delta(heads=1, kv_heads=1, dim=80, vdim=72, conv=4)]),
     "delta_key_size_128": lambda: make_config([delta(heads=2, kv_heads=2, dim=128, vdim=64, conv=4)], width=64),
     "delta_key_size_160": lambda: make_config([delta(heads=1, kv_heads=1, dim=160, vdim=24, conv=3)]),
+    "delta_key_size_272_in_shared_memory": lambda: make_config([delta(heads=2, kv_heads=1, dim=272, vdim=40, conv=2, ff=0)]),
+    "pair_memory_key_size_288": lambda: make_config([pair(mheads=1, mdim=288, mvdim=32, ff=0)]),
+    "canon_nine_taps": lambda: make_config([delta(ff=0), pair(ff=0)], taps=9),
     "pair": lambda: make_config([pair()]),
     "pair_every_head_its_own_keys": lambda: make_config([pair(heads=3, kv_heads=3, dim=12, vdim=12, rows=7, bias_max=33)]),
     "pair_ten_heads_one_key_head": lambda: make_config([pair(heads=10, kv_heads=1, dim=16, vdim=8, rows=16, bias_max=100, scale=0.6)]),
@@ -457,6 +460,21 @@ def test_long_portions_on_the_tensor_cores():
         g1, g2 = g1.cpu().numpy().reshape(2, 200, -1), g2.cpu().numpy().reshape(2, 140, -1)
         close(np.concatenate([g1[0], g2[0]]), wa, "bf16", "batch row 0")
         close(np.concatenate([g1[1], g2[1]]), wb, "bf16", "batch row 1")
+    finally:
+        r.close()
+
+
+@pytest.mark.gpu
+def test_many_heads_on_the_tensor_cores():
+    """More heads than the register form of the softmax-and-mix kernel holds: the shared-memory form, against the plain model."""
+    cfg = make_config([pair(heads=36, kv_heads=4, dim=64, vdim=128, scale=0.3, rows=9, bias_max=60, mheads=1, mdim=16, mvdim=32, ff=0)], width=128, vocab=64)
+    sd = make_nuvarax_checkpoint(cfg, "bf16", seed=77)
+    toks = tokens(150, cfg.vocab_size, seed=15)
+    want = plain(cfg, sd, toks)
+    r = Runner(cfg, sd, "bf16")
+    try:
+        close(r.run("w", toks), want, "bf16", "whole")
+        close(r.run("c", toks, cuts=[40, 110]), want, "bf16", "portions")
     finally:
         r.close()
 
