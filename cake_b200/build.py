@@ -43,6 +43,7 @@ def stale() -> bool:
 UNITS = {
     "cake_b200.o": ("cake_b200.cu", None),
     "mixers.o": ("mixers.cu", ("mixers.cuh", "common.cuh")),
+    "mixers_window.o": ("mixers_window.cu", ("mixers.cuh", "common.cuh")),
 }
 
 
@@ -103,7 +104,7 @@ def build_trace(defines=("-DMK_TRACE=1",), name="libcake_b200_trace.so") -> str:
     subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", *defines,
                            "-ccbin", "/usr/bin/g++", "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr",
                            "-I", _nccl_include(), "-I", os.path.join(ROOT, "include"), "-o", out, SRC,
-                           os.path.join(HERE, "csrc", "mixers.cu"), "-ldl"])
+                           os.path.join(HERE, "csrc", "mixers.cu"), os.path.join(HERE, "csrc", "mixers_window.cu"), "-ldl"])
     return out
 
 

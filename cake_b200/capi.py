@@ -104,7 +104,8 @@ class CRotarySpec(ctypes.Structure):
 
 class CMoeSpec(ctypes.Structure):
     """``cake_b200_moe_spec`` (include/cake_b200.h)."""
-    _fields_ = [("experts", c_int), ("identity", c_int), ("top", c_int), ("scale", c_float), ("ff", c_int), ("shared_ff", c_int), ("act", c_int)]
+    _fields_ = [("experts", c_int), ("identity", c_int), ("top", c_int), ("scale", c_float), ("ff", c_int), ("shared_ff", c_int), ("act", c_int),
+                ("limit", c_float), ("shared_limit", c_float), ("logit_bias", c_int)]
 
 
 class CMixerSpec(ctypes.Structure):
@@ -115,7 +116,9 @@ CMixerSpec._fields_ = [("kind", c_int), ("heads", c_int), ("dim", c_int), ("vdim
                        ("rot", CRotarySpec), ("decay", POINTER(c_float)), ("state", c_int), ("groups", c_int), ("conv", c_int), ("norm_groups", c_int),
                        ("moe", CMoeSpec),
                        ("kv_heads", c_int), ("bias_rows", c_int), ("bias_max", c_float), ("gate_cap", c_float), ("norm_offset", c_float),
-                       ("canon_taps", c_int), ("dense_ff", c_int), ("dense_act", c_int), ("dense_limit", c_float), ("side", POINTER(CMixerSpec))]
+                       ("canon_taps", c_int), ("dense_ff", c_int), ("dense_act", c_int), ("dense_limit", c_float), ("side", POINTER(CMixerSpec)),
+                       ("window", c_int), ("keep_first", c_int), ("qk_unit", c_int), ("q_rank", c_int), ("norm_kind", c_int), ("norm_alpha", c_float * 4),
+                       ("side_dim", c_int), ("side_col", c_int)]
 
 
 MIXER_TENSOR_FIELDS = ("norm1", "norm2", "q", "k", "v", "g", "o", "dkv", "dkv_norm", "uk", "uv", "in", "conv", "conv_b", "dt_bias", "a_log", "d",
@@ -129,18 +132,23 @@ class CMixerTensors(ctypes.Structure):
     tensors of a second mixer beside this one."""
 
 
-CMixerTensors._fields_ = [(n, POINTER(_VP) if n.startswith("e_") else _VP) for n in MIXER_TENSOR_FIELDS] + [("side", POINTER(CMixerTensors))]
+# fields behind `side` in the C struct (the newer mechanisms)
+MIXER_TENSOR_FIELDS_2 = ("sink", "dq", "dq_norm", "uq", "norm1_b", "post1_b", "norm2_b", "post2_b", "side_gate", "side_proj", "side_norm")
+CMixerTensors._fields_ = [(n, POINTER(_VP) if n.startswith("e_") else _VP) for n in MIXER_TENSOR_FIELDS] + [("side", POINTER(CMixerTensors))] + \
+                         [(n, _VP) for n in MIXER_TENSOR_FIELDS_2]
 
 
 class CEmbedTables(ctypes.Structure):
     """``cake_b200_embed_tables`` (include/cake_b200.h)."""
     _fields_ = [("bigram", _VP), ("bigram_rows", c_int), ("mul_prev", c_int), ("mul_cur", c_int), ("pos", _VP), ("pos_rows", c_int),
-                ("final_norm_offset", c_float)]
+                ("final_norm_offset", c_float), ("side", _VP), ("side_cols", c_int), ("final_norm_kind", c_int), ("final_alpha", c_float),
+                ("final_bias", _VP)]
 
 
 SYMBOLS += [
     ("cake_b200_block_load_mixer", _I, [_VP, _I, POINTER(CMixerSpec), POINTER(CMixerTensors), POINTER(_VP)]),
     ("cake_b200_stream_inject", _I, [_VP, _VP, _VP, _VP, _I, _I]),
+    ("cake_b200_stream_project", _I, [_VP, _VP, _VP, _VP, _I]),
     ("cake_b200_head_load_tables", _I, [_VP, POINTER(CEmbedTables)]),
     ("cake_b200_embed_at", _I, [_VP, _VP, POINTER(c_uint32), _I, _I, _I, _VP]),
 ]

@@ -83,10 +83,14 @@ class MoeSpec:
     scale: float = 1.0
     ff: int = 0
     shared_ff: int = 0
-    act: int = 0
+    act: int = 0             # 0 silu, 1 tanh-gelu, 2 clamped (min(g, limit) sigmoid(1.702 g) (clamp(u) + 1))
+    limit: float = 0.0
+    shared_limit: float = 0.0
+    logit_bias: bool = False  # the router's correction is a bias of the logits; choice by logit, softmax over the chosen alone
 
 
-MIXER_KINDS = {"latent_attention": 1, "retention": 2, "mamba2": 3, "delta": 4, "talking_attention": 5, "matrix_memory": 6}
+MIXER_KINDS = {"latent_attention": 1, "retention": 2, "mamba2": 3, "delta": 4, "talking_attention": 5, "matrix_memory": 6,
+               "sink_attention": 7, "latent_window": 8}
 
 
 @dataclass
@@ -121,6 +125,17 @@ class MixerSpec:
     dense_act: int = 0       # 0 silu, 1 tanh-gelu, 2 clamped (min(g, limit) sigmoid(1.702 g) (clamp(u) + 1))
     dense_limit: float = 0.0
     side: Optional["MixerSpec"] = None   # a second mixer beside this one, reading the same input
+    # sink_attention (grouped-query attention with a rotation of part of every head, unit-RMS q and k, a sliding window that keeps
+    # the first tokens and a sink) and latent_window (latent attention without positions, queries through a latent of their own,
+    # a sliding window, one gate per head), and the switches they come with: the squashing norm and the per-layer token input
+    window: int = 0          # 0 = every earlier key
+    keep_first: int = 0
+    qk_unit: bool = False
+    q_rank: int = 0
+    norm_kind: int = 0       # 0 RMS, 1 tanh(alpha x) * w + b
+    norm_alpha: list = field(default_factory=lambda: [0.0, 0.0, 0.0, 0.0])   # norm1, norm1b, norm2, norm2b (read from the checkpoint)
+    side_dim: int = 0
+    side_col: int = 0
 
     @property
     def inner(self) -> int:
@@ -167,6 +182,9 @@ class Config:
     pair_embedding: Optional[dict] = None  # {"buckets", "mul_prev", "mul_cur"}: a hashed (previous, current) token embedding is added
     learned_positions: int = 0        # > 0: a learned vector per position is added to the embedding (rows of the table)
     final_norm_offset: float = 0.0    # the final norm's gain is stored as an offset from this number
+    loop_mode: str = "step"           # in front of every pass: "step" (x += [x0] + vector), "none", "project" (x <- W [x; x0])
+    token_side_dim: int = 0           # > 0: a per-layer token input of that width (table `side.embed` [vocab, layers * dim])
+    final_norm_kind: int = 0          # 1: the final norm is the squashing norm
 
     def layer_variant(self, i: int, max_seq: Optional[int] = None) -> dict:
         """Norm placement and attention mode of layer ``i``, as the reference's per-architecture block.rs sets them up:
@@ -198,7 +216,7 @@ class Config:
     @property
     def layer_list(self) -> bool:
         """The checkpoint's config lists its layers one by one; such models keep an fp32 residual stream."""
-        return self.block_kind in ("nigenex", "setodra", "nuvarax")
+        return self.block_kind in ("nigenex", "setodra", "nuvarax", "netolorn")
 
     @property
     def scalar_final_norm(self) -> bool:
@@ -382,6 +400,77 @@ class Config:
                       pair_embedding={k: int(bg[k]) for k in ("buckets", "mul_prev", "mul_cur")} if bg else None,
                       learned_positions=npos, final_norm_offset=1.0)
 
+    @staticmethod
+    def _from_netolorn(d: dict, max_seq: int = 4096) -> "Config":
+        """Netolorn ``config.json``: ``width``, ``vocab``, ``norm.eps``, an optional ``token_side.dim``, an optional ``loop`` and
+        ``layers``, whose entries give ``type`` (``attention``: grouped-query attention with ``rot`` (dims, base, scaling), ``mask``
+        (size, keep_first), ``scale``; ``latent_attention``: ``q_rank``, ``kv_rank``, ``mask.size``, ``scale``), the mixer's sizes
+        and the feed-forward (``mlp``: kind ``dense`` with ``ff``; kind ``moe`` with ``router`` (experts, top), ``expert`` (ff, limit)
+        and an optional ``shared`` (ff, limit); or null).  Every norm is tanh(alpha x) * w + b."""
+        side = int((d.get("token_side") or {}).get("dim") or 0)
+        specs = []
+        for i, L in enumerate(d["layers"]):
+            kind, m = L.get("type"), L["mixer"]
+            mask = m.get("mask") or {}
+            if kind == "attention":
+                sp = MixerSpec(type="sink_attention", heads=int(m["heads"]), kv_heads=int(m.get("kv_heads") or m["heads"]), dim=int(m["dim"]),
+                               vdim=int(m.get("vdim") or m["dim"]), scale=float(m["scale"]), rot=RotarySpec.from_dict(m.get("rot")), qk_unit=True,
+                               window=int(mask.get("size") or 0), keep_first=int(mask.get("keep_first") or 0))
+                if sp.rot.dims % 2 or sp.rot.dims > sp.dim:
+                    raise ValueError(f"layer {i}: rot.dims {sp.rot.dims} must be even and at most dim {sp.dim}")
+            elif kind == "latent_attention":
+                sp = MixerSpec(type="latent_window", heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m.get("vdim") or m["dim"]), scale=float(m["scale"]),
+                               q_rank=int(m["q_rank"]), kv_rank=int(m["kv_rank"]), window=int(mask.get("size") or 0))
+            else:
+                raise ValueError(f"layer {i}: mixer type {kind!r} is not part of this design")
+            if sp.heads % sp.n_kv:
+                raise ValueError(f"layer {i}: {sp.heads} heads over {sp.n_kv} key heads")
+            mlp = L.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") == "dense":
+                    sp.dense_ff, sp.dense_act = int(mlp["ff"]), 0
+                elif mlp.get("kind") == "moe":
+                    r, ex, sh = mlp["router"], mlp.get("expert") or {}, mlp.get("shared")
+                    sp.moe = MoeSpec(experts=int(r["experts"]), top=int(r["top"]), ff=int(ex["ff"]), limit=float(ex["limit"]), act=2, logit_bias=True,
+                                     shared_ff=int(sh["ff"]) if sh else 0, shared_limit=float(sh["limit"]) if sh else 0.0)
+                else:
+                    raise ValueError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} is not part of this design")
+            sp.norm_kind, sp.post_norms, sp.side_dim, sp.side_col = 1, True, side, i * side
+            specs.append(sp)
+        if not specs:
+            raise ValueError("config lists no layers")
+        loop = d.get("loop") or None
+        if loop and not (0 <= int(loop["start"]) < int(loop["stop"]) <= len(specs) and int(loop["times"]) >= 1):
+            raise ValueError(f"bad loop {loop}")
+        return Config(hidden_size=int(d["width"]), intermediate_size=0, vocab_size=int(d["vocab"]), num_hidden_layers=len(specs),
+                      num_attention_heads=specs[0].heads, num_key_value_heads=specs[0].n_kv, rms_norm_eps=float(d["norm"]["eps"]),
+                      head_dim=specs[0].vdim, max_seq_len=int(max_seq), block_kind="netolorn", layers=specs, model_prefix="", loop=loop,
+                      loop_mode="project", token_side_dim=side, final_norm_kind=1)
+
+    def to_netolorn(self) -> dict:
+        """The ``config.json`` of a Netolorn Config (inverse of ``_from_netolorn``)."""
+        layers = []
+        for s in self.layers:
+            if s.type == "sink_attention":
+                mask = {"size": s.window, "keep_first": s.keep_first} if s.window else None
+                kind, m = "attention", {"heads": s.heads, "kv_heads": s.n_kv, "dim": s.dim, "vdim": s.vdim, "scale": s.scale, "rot": s.rot.to_dict(), "mask": mask}
+            else:
+                kind, m = "latent_attention", {"heads": s.heads, "dim": s.dim, "vdim": s.vdim, "scale": s.scale, "q_rank": s.q_rank, "kv_rank": s.kv_rank,
+                                               "mask": {"size": s.window} if s.window else None}
+            mo = s.moe
+            if mo is not None:
+                mlp = {"kind": "moe", "router": {"experts": mo.experts, "top": mo.top}, "expert": {"ff": mo.ff, "limit": mo.limit},
+                       "shared": {"ff": mo.shared_ff, "limit": mo.shared_limit} if mo.shared_ff else None}
+            else:
+                mlp = {"kind": "dense", "ff": s.dense_ff} if s.dense_ff else None
+            layers.append({"type": kind, "mixer": m, "mlp": mlp})
+        d = {"architecture": "Netolorn", "width": self.hidden_size, "vocab": self.vocab_size, "norm": {"eps": self.rms_norm_eps}, "layers": layers}
+        if self.token_side_dim:
+            d["token_side"] = {"dim": self.token_side_dim}
+        if self.loop:
+            d["loop"] = dict(self.loop)
+        return d
+
     def to_nuvarax(self) -> dict:
         """The ``config.json`` of a Nuvarax Config (inverse of ``_from_nuvarax``)."""
         layers = []
@@ -438,6 +527,8 @@ class Config:
             return Config._from_setodra(d)
         if d.get("architecture") == "Nuvarax":
             return Config._from_nuvarax(d)
+        if d.get("architecture") == "Netolorn":
+            return Config._from_netolorn(d)
         arch = Config.detect_arch(d)
         if arch in Config._OTHER_BLOCKS:
             raise ValueError(f"architecture {arch!r} is outside the block-forward path built here")
@@ -526,6 +617,8 @@ class Config:
             return self.to_setodra()
         if self.block_kind == "nuvarax":
             return self.to_nuvarax()
+        if self.block_kind == "netolorn":
+            return self.to_netolorn()
         d = dict(
             architectures=[arch], hidden_size=self.hidden_size, intermediate_size=self.intermediate_size,
             vocab_size=self.vocab_size, num_hidden_layers=self.num_hidden_layers,

@@ -155,6 +155,16 @@ struct cake_b200_ctx {
   void *bigram = nullptr, *pos_tab = nullptr;
   int bigram_rows = 0, mul_prev = 0, mul_cur = 0, pos_rows = 0;
   float final_norm_offset = 0.f;
+  // the per-layer token inputs of every layer side by side [vocab, side_cols]; the squashing form of the final norm; the ids of
+  // the last cake_b200_embed call stay in d_ids (d_ids_n of them) for the layers that read them
+  void *side_tab = nullptr, *ln_f_b = nullptr;
+  int side_cols = 0, final_norm_kind = 0;
+  float final_alpha = 0.f;
+  size_t d_ids_n = 0;
+  // cake_b200_stream_project: the projection [hidden, 2 hidden] and its operand [rows, 2 hidden] in D
+  void *proj_w = nullptr, *proj_ws = nullptr;
+  const void *proj_src = nullptr;
+  size_t proj_ws_cap = 0;
   // ext blocks with a side mixer: a recurrent side mixer runs on its own stream next to the main mixer (fork after the input
   // projection, join before its output projection); created on first use
   cudaStream_t side_stream = nullptr;
@@ -228,6 +238,10 @@ struct cake_b200_block {
   float *m_bias = nullptr;   // [m_bias_len, heads] fp32: the distance bias by distance
   int m_bias_len = 0;
   int pc[6] = {0, 0, 0, 0, 0, 0};
+  // sink attention / windowed latent attention; the offsets of the squashing norms; the per-layer token input
+  void *m_sink = nullptr, *m_dq_norm = nullptr, *m_uq = nullptr;
+  void *ln1_b = nullptr, *post1_b = nullptr, *ln2_b = nullptr, *post2_b = nullptr;
+  void *sd_gate = nullptr, *sd_proj = nullptr, *sd_norm = nullptr;
   bool variant() const { return !ln1 || !ln2 || pan || pfn || window >= 0 || !use_rope || ctx->cfg.pre_reshape_qk_norm; }
 };
 
@@ -578,6 +592,8 @@ extern "C" void cake_b200_ctx_destroy(cake_b200_ctx *c) {
     if (b) cudaFree(b);
   if (c->bigram) cudaFree(c->bigram);
   if (c->pos_tab) cudaFree(c->pos_tab);
+  for (void *b : {c->side_tab, c->ln_f_b, c->proj_w, c->proj_ws})
+    if (b) cudaFree(b);
   for (void *b : c->inject_vec)
     if (b) cudaFree(b);
   if (c->lm_head && c->lm_head != c->embed) cudaFree(c->lm_head);
@@ -767,7 +783,8 @@ extern "C" void cake_b200_block_free(cake_b200_block *b) {
   void *bufs[] = {b->wqkv, b->wo, b->wgu, b->wd, b->ln1, b->ln2, b->bqkv, b->qn, b->kn, b->pan, b->pfn,
                   b->w_in, b->w_out, b->g, b->shift, b->r1, b->r2, b->m_dkv_norm, b->m_uk, b->m_uv, b->m_ukt, b->m_conv, b->m_conv_b, b->m_dt_bias,
                   b->m_a_log, b->m_d, b->m_norm, b->m_router, b->m_corr, b->m_eg, b->m_ed, b->m_cos, b->m_sin, b->m_decay,
-                  b->post1, b->post2, b->canon, b->b_in, b->m_ob, b->m_talk, b->m_branch, b->m_ib, b->m_fb, b->m_bias};
+                  b->post1, b->post2, b->canon, b->b_in, b->m_ob, b->m_talk, b->m_branch, b->m_ib, b->m_fb, b->m_bias,
+                  b->m_sink, b->m_dq_norm, b->m_uq, b->ln1_b, b->post1_b, b->ln2_b, b->post2_b, b->sd_gate, b->sd_proj, b->sd_norm};
   for (void *p : bufs)
     if (p) cudaFree(p);  // cudaFree synchronises with outstanding work
   if (b->side) cake_b200_block_free(b->side);
@@ -1663,13 +1680,50 @@ static void mixer_rope_tables(const cake_b200_rotary_spec &r, int rows, std::vec
     }
 }
 
+// the routed feed-forward of a block: norm2, router rows (+ the shared expert's gate row), the stacked experts, the shared expert
+static int load_routed_ff(cake_b200_ctx *c, cake_b200_block *b, const cake_b200_moe_spec &mo, const cake_b200_mixer_tensors *t, int layer_idx) {
+  const size_t es = c->es, H = c->cfg.hidden;
+  const size_t E = mo.experts, Et = E + mo.identity, I = mo.ff, Is = mo.shared_ff;
+  RC(upload(c, &b->ln2, t->norm2, H * es));
+  // router rows, then the shared expert's gate vector as one more row, zero rows up to the tensor-core tile: one product
+  // gives every logit of a token
+  const size_t NP = (size_t)round_up((int)Et + 1, TC_BN);
+  CU(cudaMalloc(&b->m_router, NP * H * es + 16));
+  CU(cudaMemsetAsync(b->m_router, 0, NP * H * es, 0));
+  CU(cudaStreamSynchronize(0));
+  RC(pipe_copy(c, b->m_router, Et * H * es, t->router, Et * H * es, Et * H * es, 1));
+  if (Is) RC(pipe_copy(c, (char *)b->m_router + Et * H * es, H * es, t->s_sg, H * es, H * es, 1));
+  RC(upload(c, &b->m_corr, t->correction, Et * es));
+  if (E) {
+    // all experts stacked: gate / up row-interleaved per expert (as the dense blocks lay theirs out) and the down matrices,
+    // so that a grouped product addresses expert e at row e * N of one matrix
+    CU(cudaMalloc(&b->m_eg, E * 2 * I * H * es + 16));
+    CU(cudaMalloc(&b->m_ed, E * H * I * es + 16));
+    for (size_t e = 0; e < E; e++) {
+      if (!t->e_gate[e] || !t->e_up[e] || !t->e_down[e]) return fail(CAKE_B200_EINVAL, "layer %d: expert %zu has a null tensor", layer_idx, e);
+      char *gu = (char *)b->m_eg + e * 2 * I * H * es;
+      RC(pipe_copy(c, gu, 2 * H * es, t->e_gate[e], H * es, H * es, I));
+      RC(pipe_copy(c, gu + H * es, 2 * H * es, t->e_up[e], H * es, H * es, I));
+      RC(pipe_copy(c, (char *)b->m_ed + e * H * I * es, H * I * es, t->e_down[e], H * I * es, H * I * es, 1));
+    }
+  }
+  if (Is) {  // the shared expert is a dense gated feed-forward: row-interleaved gate / up as everywhere else
+    CU(cudaMalloc(&b->wgu, 2 * Is * H * es + 16));
+    RC(pipe_copy(c, b->wgu, 2 * H * es, t->s_gate, H * es, H * es, Is));
+    RC(pipe_copy(c, (char *)b->wgu + H * es, 2 * H * es, t->s_up, H * es, H * es, Is));
+    RC(upload(c, &b->wd, t->s_down, H * Is * es));
+  }
+  return CAKE_B200_OK;
+}
+
 static bool mixer_kind_ext(int kind);
 static int load_mixer_ext(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer_spec *sp, const cake_b200_mixer_tensors *t, cake_b200_block **out);
 extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer_spec *sp, const cake_b200_mixer_tensors *t,
                                           cake_b200_block **out) {
   if (!c || !sp || !t || !out) return fail(CAKE_B200_EINVAL, "null argument");
   if (!c->cfg.layer_list) return fail(CAKE_B200_EINVAL, "block_load_mixer needs a ctx created with layer_list = 1");
-  if (mixer_kind_ext(sp->kind) || sp->side || sp->norm_offset != 0.f || sp->canon_taps > 0 || sp->dense_ff > 0 || t->post1 || t->post2)
+  if (mixer_kind_ext(sp->kind) || sp->side || sp->norm_offset != 0.f || sp->canon_taps > 0 || sp->dense_ff > 0 || t->post1 || t->post2 ||
+      sp->norm_kind != 0 || sp->side_dim > 0)
     return load_mixer_ext(c, layer_idx, sp, t, out);
   const cake_b200_moe_spec &mo = sp->moe;
   const bool has_ff = mo.experts + mo.identity > 0;
@@ -1750,38 +1804,7 @@ extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const
       RC(upload(c, (void **)&b->m_sin, sn.data(), sn.size() * sizeof(float)));
       CU(cudaStreamSynchronize(c->load_stream));  // the staging copy has left the vectors
     }
-    if (has_ff) {
-      const size_t E = mo.experts, Et = E + mo.identity, I = mo.ff, Is = mo.shared_ff;
-      RC(upload(c, &b->ln2, t->norm2, H * es));
-      // router rows, then the shared expert's gate vector as one more row, zero rows up to the tensor-core tile: one product
-      // gives every logit of a token
-      const size_t NP = (size_t)round_up((int)Et + 1, TC_BN);
-      CU(cudaMalloc(&b->m_router, NP * H * es + 16));
-      CU(cudaMemsetAsync(b->m_router, 0, NP * H * es, 0));
-      CU(cudaStreamSynchronize(0));
-      RC(pipe_copy(c, b->m_router, Et * H * es, t->router, Et * H * es, Et * H * es, 1));
-      if (Is) RC(pipe_copy(c, (char *)b->m_router + Et * H * es, H * es, t->s_sg, H * es, H * es, 1));
-      RC(upload(c, &b->m_corr, t->correction, Et * es));
-      if (E) {
-        // all experts stacked: gate / up row-interleaved per expert (as the dense blocks lay theirs out) and the down matrices,
-        // so that a grouped product addresses expert e at row e * N of one matrix
-        CU(cudaMalloc(&b->m_eg, E * 2 * I * H * es + 16));
-        CU(cudaMalloc(&b->m_ed, E * H * I * es + 16));
-        for (size_t e = 0; e < E; e++) {
-          if (!t->e_gate[e] || !t->e_up[e] || !t->e_down[e]) return fail(CAKE_B200_EINVAL, "layer %d: expert %zu has a null tensor", layer_idx, e);
-          char *gu = (char *)b->m_eg + e * 2 * I * H * es;
-          RC(pipe_copy(c, gu, 2 * H * es, t->e_gate[e], H * es, H * es, I));
-          RC(pipe_copy(c, gu + H * es, 2 * H * es, t->e_up[e], H * es, H * es, I));
-          RC(pipe_copy(c, (char *)b->m_ed + e * H * I * es, H * I * es, t->e_down[e], H * I * es, H * I * es, 1));
-        }
-      }
-      if (Is) {  // the shared expert is a dense gated feed-forward: row-interleaved gate / up as everywhere else
-        CU(cudaMalloc(&b->wgu, 2 * Is * H * es + 16));
-        RC(pipe_copy(c, b->wgu, 2 * H * es, t->s_gate, H * es, H * es, Is));
-        RC(pipe_copy(c, (char *)b->wgu + H * es, 2 * H * es, t->s_up, H * es, H * es, Is));
-        RC(upload(c, &b->wd, t->s_down, H * Is * es));
-      }
-    }
+    if (has_ff) RC(load_routed_ff(c, b, mo, t, layer_idx));
     return pipe_mark(c);
   }();
   if (rc != CAKE_B200_OK) {
@@ -1795,7 +1818,10 @@ extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const
 // ------------------------------------------------------------------------------------------ ext blocks
 // Mixer-list blocks that use the structure switches of cake_b200_mixer_spec (gains stored as offsets, post norms, the input
 // convolution, a side mixer, a dense feed-forward) with the delta / talking-attention / matrix-memory mixers.
-static bool mixer_kind_ext(int kind) { return kind == CAKE_B200_MIX_DELTA || kind == CAKE_B200_MIX_TALKING_ATTENTION || kind == CAKE_B200_MIX_MATRIX_MEMORY; }
+static bool mixer_kind_ext(int kind) {
+  return kind == CAKE_B200_MIX_DELTA || kind == CAKE_B200_MIX_TALKING_ATTENTION || kind == CAKE_B200_MIX_MATRIX_MEMORY ||
+         kind == CAKE_B200_MIX_SINK_ATTENTION || kind == CAKE_B200_MIX_LATENT_WINDOW;
+}
 static int sub_kv_heads(const cake_b200_mixer_spec &sp) { return sp.kv_heads > 0 ? sp.kv_heads : sp.heads; }
 
 // bucket of a distance: exact below rows / 2, logarithmic from there up to dmax, the last bucket beyond (double precision)
@@ -1911,13 +1937,75 @@ static int load_sub_mixer(cake_b200_ctx *c, cake_b200_block *b, const cake_b200_
     RC(upload(c, &b->m_ib, t->i_b, sp->heads * es));
     RC(upload(c, &b->m_fb, t->f_b, sp->heads * es));
     RC(upload(c, &b->m_norm, t->norm, inner * es));
+  } else if (sp->kind == CAKE_B200_MIX_SINK_ATTENTION) {
+    if (!t->q || !t->k || !t->v || sp->window < 0 || sp->keep_first < 0 || sp->rot.dims < 0 || sp->rot.dims % 2 || sp->rot.dims > sp->dim ||
+        (sp->rot.dims > 0 && !(sp->rot.base > 0.0)))
+      return fail(CAKE_B200_EINVAL, "layer %d: sink attention needs q / k / v, window and keep_first >= 0 and an even rot.dims <= dim", layer_idx);
+    if (std::max(sp->dim, sp->vdim) > 768) return fail(CAKE_B200_EINVAL, "layer %d: head sizes above 768", layer_idx);
+    align8();
+    b->pc[0] = add(t->q, (size_t)sp->heads * sp->dim, t->q_b);
+    align8();
+    b->pc[1] = add(t->k, (size_t)G * sp->dim, t->k_b);
+    align8();
+    b->pc[2] = add(t->v, (size_t)G * sp->vdim, t->v_b);
+    if (t->g) {
+      align8();
+      b->pc[3] = add(t->g, inner, nullptr);
+    } else b->pc[3] = -1;
+    if (t->sink) RC(upload(c, &b->m_sink, t->sink, (size_t)sp->heads * es));
+    if (sp->rot.dims > 0) {
+      std::vector<float> cs, sn;
+      b->m_rope_rows = c->cfg.max_seq;
+      mixer_rope_tables(sp->rot, b->m_rope_rows, cs, sn);
+      RC(upload(c, (void **)&b->m_cos, cs.data(), cs.size() * sizeof(float)));
+      RC(upload(c, (void **)&b->m_sin, sn.data(), sn.size() * sizeof(float)));
+      CU(cudaStreamSynchronize(c->load_stream));  // the staging copy has left the vectors
+    }
+  } else if (sp->kind == CAKE_B200_MIX_LATENT_WINDOW) {
+    if (sp->q_rank < 1 || sp->kv_rank < 1 || sp->kv_rank > 768 || sp->window < 0 || sp->keep_first < 0 || !t->dq || !t->dq_norm || !t->uq || !t->dkv ||
+        !t->dkv_norm || !t->uk || !t->uv)
+      return fail(CAKE_B200_EINVAL, "layer %d: windowed latent attention needs q_rank, kv_rank <= 768 and dq / dq_norm / uq / dkv / dkv_norm / uk / uv", layer_idx);
+    if (G != sp->heads) return fail(CAKE_B200_EINVAL, "layer %d: latent attention expands keys for every head", layer_idx);
+    align8();
+    b->pc[0] = add(t->dq, (size_t)sp->q_rank, nullptr);
+    align8();
+    b->pc[1] = add(t->dkv, (size_t)sp->kv_rank, nullptr);
+    if (t->g) {
+      align8();
+      b->pc[3] = add(t->g, (size_t)sp->heads, nullptr);
+    } else b->pc[3] = -1;
+    RC(upload(c, &b->m_dq_norm, t->dq_norm, (size_t)sp->q_rank * es));
+    RC(upload(c, &b->m_uq, t->uq, (size_t)sp->heads * sp->dim * sp->q_rank * es));
+    RC(upload(c, &b->m_dkv_norm, t->dkv_norm, (size_t)sp->kv_rank * es));
+    RC(upload(c, &b->m_uk, t->uk, (size_t)sp->heads * sp->dim * sp->kv_rank * es));
+    RC(upload(c, &b->m_uv, t->uv, inner * sp->kv_rank * es));
   } else return fail(CAKE_B200_EINVAL, "layer %d: mixer kind %d is not built with these block switches", layer_idx, sp->kind);
   return CAKE_B200_OK;
 }
 
 static int load_mixer_ext(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer_spec *sp, const cake_b200_mixer_tensors *t, cake_b200_block **out) {
   if (!t->norm1) return fail(CAKE_B200_EINVAL, "layer %d: null norm1", layer_idx);
-  if (sp->moe.experts + sp->moe.identity > 0) return fail(CAKE_B200_EINVAL, "layer %d: the routed feed-forward is not built for this block structure", layer_idx);
+  const cake_b200_moe_spec &mo = sp->moe;
+  const bool has_moe = mo.experts + mo.identity > 0;
+  if (has_moe) {
+    if (sp->side || sp->canon_taps > 0 || sp->norm_offset != 0.f || sp->dense_ff > 0)
+      return fail(CAKE_B200_EINVAL, "layer %d: the routed feed-forward is not built beside a side mixer, an input convolution, offset gains or a dense feed-forward", layer_idx);
+    if (mo.experts < 0 || mo.identity < 0 || mo.top < 1 || mo.top > mo.experts + mo.identity || mo.top > 32 || mo.experts + mo.identity > 256 ||
+        (mo.experts > 0 && mo.ff < 1) || mo.shared_ff < 0 || mo.act < 0 || mo.act > 2 || !t->norm2 || !t->router || !t->correction)
+      return fail(CAKE_B200_EINVAL, "layer %d: bad router sizes (top <= 32, experts + identity <= 256) or null norm2 / router / correction", layer_idx);
+    if (mo.experts > 0 && (!t->e_gate || !t->e_up || !t->e_down)) return fail(CAKE_B200_EINVAL, "layer %d: null expert table", layer_idx);
+    if (mo.shared_ff > 0 && (!t->s_gate || !t->s_up || !t->s_down || !t->s_sg)) return fail(CAKE_B200_EINVAL, "layer %d: null shared-expert pointer", layer_idx);
+  }
+  if (sp->norm_kind < 0 || sp->norm_kind > 1) return fail(CAKE_B200_EINVAL, "layer %d: norm_kind %d", layer_idx, sp->norm_kind);
+  if (sp->norm_kind == 1) {
+    const bool has_ff = has_moe || sp->dense_ff > 0;
+    if (sp->side || sp->canon_taps > 0 || sp->norm_offset != 0.f)
+      return fail(CAKE_B200_EINVAL, "layer %d: the squashing norm is not built beside a side mixer, an input convolution or offset gains", layer_idx);
+    if (!t->norm1_b || (t->post1 && !t->post1_b) || (has_ff && (!t->norm2_b || (t->post2 && !t->post2_b))))
+      return fail(CAKE_B200_EINVAL, "layer %d: the squashing norm needs an offset vector beside every gain", layer_idx);
+  }
+  if (sp->side_dim < 0 || sp->side_col < 0 || (sp->side_dim > 0 && (!t->side_gate || !t->side_proj || !t->side_norm)))
+    return fail(CAKE_B200_EINVAL, "layer %d: a token input needs side_gate / side_proj / side_norm", layer_idx);
   if (sp->side && (!t->side || !t->branch_norm || !t->side->branch_norm)) return fail(CAKE_B200_EINVAL, "layer %d: a side mixer needs its tensors and both branch norms", layer_idx);
   if (sp->canon_taps < 0 || (sp->canon_taps > 0 && !t->canon)) return fail(CAKE_B200_EINVAL, "layer %d: canon_taps %d without canon", layer_idx, sp->canon_taps);
   if (sp->dense_ff < 0 || (sp->dense_ff > 0 && (!t->ff_gate || !t->ff_up || !t->ff_down || !t->norm2 || sp->dense_act < 0 || sp->dense_act > 2)))
@@ -1942,7 +2030,11 @@ static int load_mixer_ext(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer
     b->ms.dense_ff = sp->dense_ff;
     b->ms.dense_act = sp->dense_act;
     b->ms.dense_limit = sp->dense_limit;
-    b->ms.moe = cake_b200_moe_spec{};
+    b->ms.moe = has_moe ? mo : cake_b200_moe_spec{};
+    b->ms.norm_kind = sp->norm_kind;
+    for (int i = 0; i < 4; i++) b->ms.norm_alpha[i] = sp->norm_alpha[i];
+    b->ms.side_dim = sp->side_dim;
+    b->ms.side_col = sp->side_col;
     b->n_in = (int)row;
     b->n_in_pad = round_up(b->n_in, b->n_in > 1024 ? 256 : TC_BN);
     CU(cudaMalloc(&b->w_in, (size_t)b->n_in_pad * H * es + 16));
@@ -1972,6 +2064,23 @@ static int load_mixer_ext(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer
       RC(pipe_copy(c, (char *)b->wgu + H * es, 2 * H * es, t->ff_up, H * es, H * es, I));
       RC(upload(c, &b->wd, t->ff_down, H * I * es));
     }
+    if (has_moe) {
+      RC(load_routed_ff(c, b, mo, t, layer_idx));
+      if (t->post2) RC(upload(c, &b->post2, t->post2, H * es));
+    }
+    if (sp->norm_kind == 1) {
+      RC(upload(c, &b->ln1_b, t->norm1_b, H * es));
+      if (t->post1) RC(upload(c, &b->post1_b, t->post1_b, H * es));
+      if (has_moe || sp->dense_ff > 0) {
+        RC(upload(c, &b->ln2_b, t->norm2_b, H * es));
+        if (t->post2) RC(upload(c, &b->post2_b, t->post2_b, H * es));
+      }
+    }
+    if (sp->side_dim > 0) {
+      RC(upload(c, &b->sd_gate, t->side_gate, (size_t)sp->side_dim * H * es));
+      RC(upload(c, &b->sd_proj, t->side_proj, H * sp->side_dim * es));
+      RC(upload(c, &b->sd_norm, t->side_norm, H * es));
+    }
     return pipe_mark(c);
   }();
   if (rc != CAKE_B200_OK) {
@@ -1999,14 +2108,17 @@ static int cache_ensure_sub(cake_b200_cache *k, int slot, const cake_b200_block 
   cake_b200_ctx *c = k->ctx;
   const cake_b200_mixer_spec &sp = b->ms;
   const int G = sp.kv_heads, tag = sp.kind;
-  const int width = sp.kind == CAKE_B200_MIX_TALKING_ATTENTION ? G * (sp.dim + sp.vdim) : sp.heads * sp.dim * sp.vdim;
+  const bool kv_rows = sp.kind == CAKE_B200_MIX_TALKING_ATTENTION || sp.kind == CAKE_B200_MIX_SINK_ATTENTION;
+  const int width = kv_rows ? G * (sp.dim + sp.vdim) : sp.kind == CAKE_B200_MIX_LATENT_WINDOW ? sp.kv_rank : sp.heads * sp.dim * sp.vdim;
   if (k->kv_heads[slot] && (k->kv_heads[slot] != tag || k->kv_hd[slot] != width))
     return fail(CAKE_B200_ESTATE, "cache entry %d was used with another layer geometry", slot);
   if (k->kv_heads[slot]) return CAKE_B200_OK;
-  if (sp.kind == CAKE_B200_MIX_TALKING_ATTENTION) {
+  if (kv_rows) {
     CU(cudaMalloc(&k->k[slot], (size_t)k->batch * G * k->cap * sp.dim * c->es + 16));
     CU(cudaMalloc(&k->v[slot], (size_t)k->batch * G * k->cap * sp.vdim * c->es + 16));
     if (talk_on_tc(c, b)) CU(cudaMalloc(&k->vt[slot], (size_t)k->batch * G * sp.vdim * latent_cap_t(k->cap) * c->es + 16));
+  } else if (sp.kind == CAKE_B200_MIX_LATENT_WINDOW) {  // the normed latent: one row per position for all heads
+    CU(cudaMalloc(&k->k[slot], (size_t)k->batch * k->cap * sp.kv_rank * c->es + 16));
   } else {
     CU(cudaMalloc(&k->rec_state[slot], (size_t)k->batch * width * sizeof(float)));
     if (sp.kind == CAKE_B200_MIX_DELTA && sp.conv > 1)
@@ -2029,17 +2141,36 @@ static int cache_ensure_ext(cake_b200_cache *k, int layer, const cake_b200_block
 
 // scratch of one mixer of an ext block
 struct SubScratch {
-  void *att, *conv, *qh, *pw, *oh;
+  void *att, *conv, *qh, *pw, *oh, *cq, *qa, *lat;
   float *o32, *qn, *kn, *f1, *f2, *f3, *part, *y, *scores, *stats;
   int nsplit, tc_tok;
 };
 constexpr int TALK_SPLIT_MAX = 64;
+constexpr int WIN_SPLIT_MAX = 32;
 template <typename Take> static SubScratch sub_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, int S, int n_keys, Take &&take) {
   SubScratch s{};
   const cake_b200_mixer_spec &sp = b->ms;
   const size_t es = c->es, inner = (size_t)sp.heads * sp.vdim, G = sp.kv_heads;
   s.att = take(M * inner * es);
   s.y = (float *)take(M * c->cfg.hidden * sizeof(float));
+  if (sp.kind == CAKE_B200_MIX_SINK_ATTENTION || sp.kind == CAKE_B200_MIX_LATENT_WINDOW) {
+    const bool latent = sp.kind == CAKE_B200_MIX_LATENT_WINDOW;
+    const size_t vd = latent ? sp.kv_rank : sp.vdim;
+    s.qh = take(M * sp.heads * sp.dim * es);  // rotated unit queries / the expanded queries
+    if (latent) {
+      s.cq = take(M * sp.q_rank * es);
+      s.qa = take(M * sp.heads * sp.kv_rank * es);
+      s.lat = take(M * sp.heads * sp.kv_rank * es);
+    }
+    // steps of a few rows over many visible keys: split the keys so that the step fills the chip
+    const int vis = std::min(n_keys, sp.window > 0 ? sp.window + sp.keep_first : n_keys);
+    if (M * sp.heads <= 1024 && vis >= 256) {
+      s.nsplit = (int)std::min<size_t>(WIN_SPLIT_MAX, std::min<size_t>((vis + 63) / 64, (2 * (size_t)c->sm_count + M * sp.heads - 1) / (M * sp.heads)));
+      if (s.nsplit > 1) s.part = (float *)take(M * sp.heads * s.nsplit * (vd + 2) * sizeof(float));
+      else s.nsplit = 0;
+    }
+    return s;
+  }
   if (sp.kind == CAKE_B200_MIX_TALKING_ATTENTION) {
     if (talk_on_tc(c, b) && (size_t)S * sp.heads >= TALK_TC_MIN_ROWS) {  // blocks of tc_tok tokens of one batch row as matrix products
       const size_t kp = ((size_t)n_keys + TC_BN - 1) / TC_BN * TC_BN;
@@ -2073,10 +2204,21 @@ template <typename Take> static SubScratch sub_scratch(const cake_b200_ctx *c, c
   } else s.f3 = (float *)take(M * sp.heads * sizeof(float));
   return s;
 }
+struct MoeScratch {
+  void *act, *sact, *sorted;
+  float *wts, *sgate, *y, *logits;
+  int *ids, *counts, *perm, *pos_of, *tile_expert;
+  int max_tiles, tile;
+};
+static bool moe_on_tc(const cake_b200_ctx *c, const cake_b200_block *b);
+template <typename Take> static MoeScratch moe_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, Take &&take);
+template <typename T>
+static int enqueue_routed_ff(cake_b200_ctx *c, const cake_b200_block *b, const MoeScratch &w, const void *h, const float *x, float *out, int M, uint64_t *lc);
 struct ExtScratch {
   void *h, *proj, *act;
   float *h32;
   SubScratch a, b;
+  MoeScratch moe;
   size_t total;
 };
 static ExtScratch ext_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, char *base, int S, int n_keys) {
@@ -2094,6 +2236,7 @@ static ExtScratch ext_scratch(const cake_b200_ctx *c, const cake_b200_block *b, 
   s.a = sub_scratch(c, b, M, S, n_keys, take);
   if (b->side) s.b = sub_scratch(c, b->side, M, S, n_keys, take);
   if (b->ms.dense_ff > 0) s.act = take(M * (size_t)b->ms.dense_ff * es);
+  s.moe = moe_scratch(c, b, M, take);
   s.total = off;
   return s;
 }
@@ -2164,6 +2307,36 @@ static int run_sub_mixer(cake_b200_ctx *c, const cake_b200_block *b, cake_b200_c
                       w.att, B, S, sp.heads, G, sp.dim, sp.vdim, kc->cap, pos0, sp.scale, w.part, w.nsplit};
       MX(mx::talk_attention(st, dt, ta, lc));
     }
+  } else if (sp.kind == CAKE_B200_MIX_SINK_ATTENTION) {
+    mx::QkPrep qp{proj, ldp, b->pc[0], b->pc[1], b->pc[2], b->m_cos, b->m_sin, sp.rot.dims, sp.qk_unit, c->cfg.rms_eps, w.qh, kc->k[slot], kc->v[slot],
+                  B, S, sp.heads, G, sp.dim, sp.vdim, kc->cap, pos0};
+    MX(mx::qk_prep(st, dt, qp, lc));
+    mx::WindowAttn wa{w.qh, sp.heads * sp.dim, kc->k[slot], kc->v[slot], b->pc[3] >= 0 ? proj + b->pc[3] : nullptr, ldp, 0, b->m_sink, w.att, inner,
+                      B, S, sp.heads, G, sp.dim, sp.vdim, kc->cap, pos0, sp.window, sp.keep_first, sp.scale, w.part, w.nsplit};
+    if (mx::window_attention_tiled_ok(dt, wa)) MX(mx::window_attention_tiled(st, dt, wa, lc));
+    else MX(mx::window_attention(st, dt, wa, lc));
+  } else if (sp.kind == CAKE_B200_MIX_LATENT_WINDOW) {
+    // both latents are normed (the key / value latent straight into the cache), the query latent is expanded and taken through
+    // the key expansion, so that the attention runs over the cached latent rows for all heads: qa_h = uk_h^T q_h,
+    // lat_h = sum_j w_hj c_j, att_h = uv_h lat_h
+    const int R = sp.kv_rank;
+    mx::RmsCols nq{proj, ldp, b->pc[0], b->m_dq_norm, w.cq, sp.q_rank, S, 0, M, S, sp.q_rank, c->cfg.rms_eps};
+    MX(mx::rms_cols(st, dt, nq, lc));
+    mx::RmsCols nk{proj, ldp, b->pc[1], b->m_dkv_norm, kc->k[slot], R, kc->cap, pos0, M, S, R, c->cfg.rms_eps};
+    MX(mx::rms_cols(st, dt, nk, lc));
+    if (listed_tc<T>(c, M, sp.heads * sp.dim, sp.q_rank)) RC((listed_gemm_tc<T, TCE_PLAIN>(c, w.cq, b->m_uq, nullptr, w.qh, M, sp.heads * sp.dim, sp.q_rank, 0, 0)));
+    else {
+      RowsGemm gq{w.cq, b->m_uq, nullptr, w.qh, M, sp.heads * sp.dim, sp.q_rank, sp.q_rank, sp.heads * sp.dim, 0, 0.f};
+      RC((gemm_rows_T<T, RE_STORE>(c, gq)));
+    }
+    mx::HeadGemm ga{w.qh, b->m_uk, w.qa, M, R, sp.dim, sp.heads, sp.dim, (long)sp.dim * R, R, sp.heads * sp.dim, R, sp.heads * R, 1};
+    MX(mx::head_gemm(st, dt, ga, lc));
+    mx::WindowAttn wa{w.qa, sp.heads * R, kc->k[slot], kc->k[slot], b->pc[3] >= 0 ? proj + b->pc[3] : nullptr, ldp, 1, nullptr, w.lat, sp.heads * R,
+                      B, S, sp.heads, 1, R, R, kc->cap, pos0, sp.window, sp.keep_first, sp.scale, w.part, w.nsplit};
+    if (mx::window_attention_tiled_ok(dt, wa)) MX(mx::window_attention_tiled(st, dt, wa, lc));
+    else MX(mx::window_attention(st, dt, wa, lc));
+    mx::HeadGemm gv{w.lat, b->m_uv, w.att, M, sp.vdim, R, sp.heads, R, (long)sp.vdim * R, sp.vdim, sp.heads * R, R, inner, 0};
+    MX(mx::head_gemm(st, dt, gv, lc));
   } else {
     const float qs = 1.0f / sqrtf((float)sp.dim);
     mx::GatePrep gp{proj + b->pc[0], proj + b->pc[1], ldp, proj + b->pc[4], proj + b->pc[5], ldp, b->m_ib, b->m_fb, kc->rec_aux[slot], w.f1, w.f2, w.f3,
@@ -2188,8 +2361,14 @@ static int enqueue_ext_layer(cake_b200_ctx *c, const cake_b200_block *b, int l, 
   cudaStream_t st = c->stream;
   const ExtScratch w = ext_scratch(c, b, (size_t)M, (char *)c->mx_ws, S, pos0 + S);
   // 1. h = norm1(x), the input convolution, every projection of the mixer(s) in one product
-  mx::RmsRows n1{cur, b->ln1, sp.norm_offset, sp.canon_taps > 0 ? w.h32 : nullptr, sp.canon_taps > 0 ? nullptr : w.h, M, H, eps};
-  MX(mx::rms_rows(st, dt, n1, lc));
+  const bool squash = sp.norm_kind == 1;  // tanh(alpha x) * w + b instead of an RMS norm, in all four places
+  if (squash) {
+    mx::TanhNorm n1{cur, nullptr, 1, 0, b->ln1, b->ln1_b, sp.norm_alpha[0], nullptr, nullptr, w.h, M, H};
+    MX(mx::tanh_norm(st, dt, n1, lc));
+  } else {
+    mx::RmsRows n1{cur, b->ln1, sp.norm_offset, sp.canon_taps > 0 ? w.h32 : nullptr, sp.canon_taps > 0 ? nullptr : w.h, M, H, eps};
+    MX(mx::rms_rows(st, dt, n1, lc));
+  }
   if (sp.canon_taps > 0) {
     mx::CanonConv cc{w.h32, b->canon, kc->canon_hist[l], w.h, B, S, H, sp.canon_taps, pos0};
     MX(mx::canon_conv(st, dt, cc, lc));
@@ -2219,22 +2398,59 @@ static int enqueue_ext_layer(cake_b200_ctx *c, const cake_b200_block *b, int l, 
     RC(gemm_f32_out<T>(c, w.b.att, b->side->wo, w.b.y, M, H, b->side->ms.heads * b->side->ms.vdim));
   } else if (b->side) RC(run_sub_mixer<T>(c, b->side, kc, nl + l, w.b, (const T *)w.proj, b->n_in_pad, B, S, pos0, lc, st, true));
   // 3. x <- x + post1(branches)
-  mx::BranchMerge bm{w.a.y, b->side ? w.b.y : nullptr, b->m_ob, b->side ? b->side->m_ob : nullptr, b->m_branch, b->side ? b->side->m_branch : nullptr,
-                     b->post1, sp.norm_offset, cur, x_out, M, H, eps};
-  MX(mx::branch_merge(st, dt, bm, lc));
+  if (squash && b->post1) {
+    mx::TanhNorm p1{w.a.y, nullptr, 1, 0, b->post1, b->post1_b, sp.norm_alpha[1], cur, x_out, nullptr, M, H};
+    MX(mx::tanh_norm(st, dt, p1, lc));
+  } else {
+    mx::BranchMerge bm{w.a.y, b->side ? w.b.y : nullptr, b->m_ob, b->side ? b->side->m_ob : nullptr, b->m_branch, b->side ? b->side->m_branch : nullptr,
+                       b->post1, sp.norm_offset, cur, x_out, M, H, eps};
+    MX(mx::branch_merge(st, dt, bm, lc));
+  }
   // 4. x <- x + post2(ff(norm2(x)))
+  const bool has_moe = sp.moe.experts + sp.moe.identity > 0;
+  if (sp.dense_ff > 0 || has_moe) {
+    if (squash) {
+      mx::TanhNorm n2{x_out, nullptr, 1, 0, b->ln2, b->ln2_b, sp.norm_alpha[2], nullptr, nullptr, w.h, M, H};
+      MX(mx::tanh_norm(st, dt, n2, lc));
+    } else {
+      mx::RmsRows n2{x_out, b->ln2, sp.norm_offset, nullptr, w.h, M, H, eps};
+      MX(mx::rms_rows(st, dt, n2, lc));
+    }
+  }
+  if (has_moe) {  // the feed-forward's sum lands in y; a post norm squashes it on its way into the stream
+    if (b->post2) {
+      RC(enqueue_routed_ff<T>(c, b, w.moe, w.h, nullptr, w.a.y, M, lc));
+      if (squash) {
+        mx::TanhNorm p2{w.a.y, nullptr, 1, 0, b->post2, b->post2_b, sp.norm_alpha[3], x_out, x_out, nullptr, M, H};
+        MX(mx::tanh_norm(st, dt, p2, lc));
+      } else {
+        mx::BranchMerge fm{w.a.y, nullptr, nullptr, nullptr, nullptr, nullptr, b->post2, sp.norm_offset, x_out, x_out, M, H, eps};
+        MX(mx::branch_merge(st, dt, fm, lc));
+      }
+    } else RC(enqueue_routed_ff<T>(c, b, w.moe, w.h, x_out, x_out, M, lc));
+  }
   if (sp.dense_ff > 0) {
     const int I = sp.dense_ff;
-    mx::RmsRows n2{x_out, b->ln2, sp.norm_offset, nullptr, w.h, M, H, eps};
-    MX(mx::rms_rows(st, dt, n2, lc));
     if (listed_tc<T>(c, M, 2 * I, H)) RC((listed_gemm_tc<T, TCE_SWIGLU>(c, w.h, b->wgu, nullptr, w.act, M, 2 * I, H, sp.dense_act, I, sp.dense_limit)));
     else {
       RowsGemm gu{w.h, b->wgu, nullptr, w.act, M, 2 * I, H, H, I, sp.dense_act, sp.dense_limit};
       RC((gemm_rows_T<T, RE_GATE_UP>(c, gu)));
     }
     RC(gemm_f32_out<T>(c, w.act, b->wd, w.a.y, M, H, I));
-    mx::BranchMerge fm{w.a.y, nullptr, nullptr, nullptr, nullptr, nullptr, b->post2, sp.norm_offset, x_out, x_out, M, H, eps};
-    MX(mx::branch_merge(st, dt, fm, lc));
+    if (squash && b->post2) {
+      mx::TanhNorm p2{w.a.y, nullptr, 1, 0, b->post2, b->post2_b, sp.norm_alpha[3], x_out, x_out, nullptr, M, H};
+      MX(mx::tanh_norm(st, dt, p2, lc));
+    } else {
+      mx::BranchMerge fm{w.a.y, nullptr, nullptr, nullptr, nullptr, nullptr, b->post2, sp.norm_offset, x_out, x_out, M, H, eps};
+      MX(mx::branch_merge(st, dt, fm, lc));
+    }
+  }
+  // 5. the per-layer token input
+  if (sp.side_dim > 0) {
+    if (!c->side_tab || sp.side_col + sp.side_dim > c->side_cols) return fail(CAKE_B200_ESTATE, "layer %d: the token input needs columns %d..%d of the side table (%d loaded)", b->layer, sp.side_col, sp.side_col + sp.side_dim, c->side_cols);
+    if (c->d_ids_n != (size_t)M) return fail(CAKE_B200_ESTATE, "layer %d: the token input needs the ids of this step (%zu embedded, %d rows)", b->layer, c->d_ids_n, M);
+    mx::TokenSide ts{x_out, x_out, c->d_ids, c->side_tab, c->side_cols, sp.side_col, b->sd_gate, b->sd_proj, b->sd_norm, M, H, sp.side_dim, eps};
+    MX(mx::token_side(st, dt, ts, lc));
   }
   return CAKE_B200_OK;
 }
@@ -2266,11 +2482,10 @@ static int cache_ensure_mixer(cake_b200_cache *k, int layer, const cake_b200_blo
 
 // scratch of one block for M rows, carved from the ctx arena (base == nullptr: sizes only)
 struct MixerScratch {
-  void *h, *proj, *qa, *lat, *att, *conv, *act, *sact, *sorted, *pw;
-  float *o32, *wts, *sgate, *y, *part, *scores, *logits;
+  void *h, *proj, *qa, *lat, *att, *conv, *pw;
+  float *o32, *part, *scores;
   int nsplit, lat_tok;
-  int *ids, *counts, *perm, *pos_of, *tile_expert;
-  int max_tiles, tile;
+  MoeScratch moe;
   size_t total;
 };
 // the routed experts of a block run as grouped products on the tensor cores when D is 16-bit and the tiles cover the shapes
@@ -2278,6 +2493,30 @@ static bool moe_on_tc(const cake_b200_ctx *c, const cake_b200_block *b) {
   static const bool no_tc = []() { const char *e = getenv("CAKE_B200_NO_TC"); return e && e[0] == '1'; }();
   const cake_b200_moe_spec &mo = b->ms.moe;
   return !no_tc && c->cfg.dtype != CAKE_B200_F32 && mo.experts > 0 && c->cfg.hidden % 128 == 0 && mo.ff % 64 == 0;
+}
+template <typename Take> static MoeScratch moe_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, Take &&take) {
+  MoeScratch s{};
+  const cake_b200_moe_spec &mo = b->ms.moe;
+  if (mo.experts + mo.identity < 1) return s;
+  const size_t es = c->es, H = c->cfg.hidden, nt = M * mo.top;
+  s.tile = moe_on_tc(c, b) ? TC_BM : 64;
+  s.max_tiles = (int)((nt + s.tile - 1) / s.tile + std::min<size_t>(mo.experts, nt));
+  const size_t rows = (size_t)s.max_tiles * s.tile;
+  s.logits = (float *)take(M * (size_t)round_up(mo.experts + mo.identity + 1, TC_BN) * sizeof(float));
+  s.ids = (int *)take(nt * sizeof(int));
+  s.wts = (float *)take(nt * sizeof(float));
+  s.sgate = (float *)take(M * sizeof(float));
+  s.counts = (int *)take((mo.experts + 1) * sizeof(int));
+  s.perm = (int *)take(rows * sizeof(int));
+  s.pos_of = (int *)take(nt * sizeof(int));
+  s.tile_expert = (int *)take(s.max_tiles * sizeof(int));
+  if (mo.experts) {
+    s.act = take(rows * mo.ff * es);
+    s.y = (float *)take(rows * H * sizeof(float));
+    if (s.tile == TC_BM) s.sorted = take(rows * H * es);
+  }
+  if (mo.shared_ff) s.sact = take(M * mo.shared_ff * es);
+  return s;
 }
 static MixerScratch mixer_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, char *base, int S = 1, int n_keys = 1) {
   MixerScratch s{};
@@ -2308,29 +2547,51 @@ static MixerScratch mixer_scratch(const cake_b200_ctx *c, const cake_b200_block 
     s.o32 = (float *)take(M * inner * sizeof(float));
     if (sp.kind == CAKE_B200_MIX_STATE_SPACE) s.conv = take(M * (inner + 2 * (size_t)sp.groups * sp.state) * es);
   }
-  const cake_b200_moe_spec &mo = sp.moe;
-  if (mo.experts + mo.identity > 0) {
-    const size_t nt = M * mo.top;
-    s.tile = moe_on_tc(c, b) ? TC_BM : 64;
-    s.max_tiles = (int)((nt + s.tile - 1) / s.tile + std::min<size_t>(mo.experts, nt));
-    const size_t rows = (size_t)s.max_tiles * s.tile;
-    s.logits = (float *)take(M * (size_t)round_up(mo.experts + mo.identity + 1, TC_BN) * sizeof(float));
-    s.ids = (int *)take(nt * sizeof(int));
-    s.wts = (float *)take(nt * sizeof(float));
-    s.sgate = (float *)take(M * sizeof(float));
-    s.counts = (int *)take((mo.experts + 1) * sizeof(int));
-    s.perm = (int *)take(rows * sizeof(int));
-    s.pos_of = (int *)take(nt * sizeof(int));
-    s.tile_expert = (int *)take(s.max_tiles * sizeof(int));
-    if (mo.experts) {
-      s.act = take(rows * mo.ff * es);
-      s.y = (float *)take(rows * H * sizeof(float));
-      if (s.tile == TC_BM) s.sorted = take(rows * H * es);
-    }
-    if (mo.shared_ff) s.sact = take(M * mo.shared_ff * es);
-  }
+  s.moe = moe_scratch(c, b, M, take);
   s.total = off;
   return s;
+}
+
+// The routed feed-forward on normed rows h [M, hidden] in D: out = (x ? x : 0) + sum over a token's chosen experts of weight *
+// expert(h) (+ weight * h for identity experts) + sigmoid(shared gate) * shared expert(h); out may alias x.
+template <typename T>
+static int enqueue_routed_ff(cake_b200_ctx *c, const cake_b200_block *b, const MoeScratch &w, const void *h, const float *x, float *out, int M, uint64_t *lc) {
+  const cake_b200_moe_spec &mo = b->ms.moe;
+  const int H = c->cfg.hidden, dt = c->cfg.dtype;
+  cudaStream_t st = c->stream;
+  const int NP = round_up(mo.experts + mo.identity + 1, TC_BN);
+  RowsGemm gr{h, b->m_router, nullptr, w.logits, M, NP, H, H, NP, 0, 0.f};
+  if (listed_tc<T>(c, M, NP, H)) RC((listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, h, b->m_router, nullptr, w.logits, M, NP, H, 0, 0)));
+  else RC((gemm_rows_T<T, RE_SOFTCAP_F32>(c, gr)));
+  mx::MoePlan mp{w.logits, NP, b->m_corr, mo.shared_ff ? 1 : 0, M, H, mo.experts, mo.identity, mo.top, mo.scale, w.ids, w.wts,
+                 w.sgate, w.tile, w.counts, w.perm, w.pos_of, w.tile_expert, w.max_tiles, mo.logit_bias};
+  MX(mx::moe_route(st, dt, mp, lc));
+  if (mo.experts && w.sorted) {  // grouped products: sorted rows of h -> act(gate) * up -> down, expert e at row e * N of the stacked weights
+    const int rows = w.max_tiles * w.tile;
+    MX(mx::moe_gather(st, dt, h, w.perm, w.sorted, rows, H, mo.top, lc));
+    TcExtra xg;
+    xg.tile_group = w.tile_expert;
+    xg.n_groups = mo.experts;
+    RC((listed_gemm_tc<T, TCE_SWIGLU>(c, w.sorted, b->m_eg, nullptr, w.act, rows, 2 * mo.ff, H, mo.act, mo.ff, mo.limit, xg)));
+    RC((listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, w.act, b->m_ed, nullptr, w.y, rows, H, mo.ff, 0, 0, 0.f, xg)));
+  } else if (mo.experts) {
+    mx::MoeExperts me{h, b->m_eg, b->m_ed, w.act, w.y, M, H, mo.ff, mo.top, mo.act, w.perm, w.tile_expert, w.tile, w.max_tiles, mo.limit};
+    MX(mx::moe_experts(st, dt, me, lc));
+  }
+  mx::MoeCombine mc{x, out, h, w.y, w.wts, w.ids, w.pos_of, M, H, mo.top, mo.experts};
+  MX(mx::moe_combine(st, dt, mc, lc));
+  if (mo.shared_ff) {
+    RowsGemm gu{h, b->wgu, nullptr, w.sact, M, 2 * mo.shared_ff, H, H, mo.shared_ff, mo.act, mo.shared_limit};
+    if (listed_tc<T>(c, M, 2 * mo.shared_ff, H)) RC((listed_gemm_tc<T, TCE_SWIGLU>(c, h, b->wgu, nullptr, w.sact, M, 2 * mo.shared_ff, H, mo.act, mo.shared_ff, mo.shared_limit)));
+    else RC((gemm_rows_T<T, RE_GATE_UP>(c, gu)));
+    RowsGemm gd{w.sact, b->wd, out, out, M, H, mo.shared_ff, mo.shared_ff, H, 0, 0.f, w.sgate};
+    if (listed_tc<T>(c, M, H, mo.shared_ff) && ((uintptr_t)out & 15) == 0) {
+      TcExtra xs;
+      xs.row_scale = w.sgate;
+      RC((listed_gemm_tc<T, TCE_RESIDUAL_F32>(c, w.sact, b->wd, out, out, M, H, mo.shared_ff, 0, 0, 0.f, xs)));
+    } else RC((gemm_rows_T<T, RE_RESIDUAL_F32>(c, gd)));
+  }
+  return CAKE_B200_OK;
 }
 
 // x_in, x_out: [B, S, hidden] fp32 (may alias)
@@ -2452,42 +2713,10 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
       else RC((gemm_rows_T<T, RE_RESIDUAL_F32>(c, go)));
       cur = x_out;
       // 4. x <- x + routed experts(norm2(x)) + gate * shared expert
-      const cake_b200_moe_spec &mo = sp.moe;
-      if (mo.experts + mo.identity > 0) {
+      if (sp.moe.experts + sp.moe.identity > 0) {
         RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, 1, 0, (const T *)b->ln2, 1, (const T *)nullptr,
                       (const float *)nullptr, (float *)nullptr, (T *)w.h, (T *)nullptr, S, H, c->cfg.rms_eps, pos0, 0.f));
-        const int NP = round_up(mo.experts + mo.identity + 1, TC_BN);
-        RowsGemm gr{w.h, b->m_router, nullptr, w.logits, M, NP, H, H, NP, 0, 0.f};
-        if (listed_tc<T>(c, M, NP, H)) RC((listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, w.h, b->m_router, nullptr, w.logits, M, NP, H, 0, 0)));
-        else RC((gemm_rows_T<T, RE_SOFTCAP_F32>(c, gr)));
-        mx::MoePlan mp{w.logits, NP, b->m_corr, mo.shared_ff ? 1 : 0, M, H, mo.experts, mo.identity, mo.top, mo.scale, w.ids, w.wts,
-                       w.sgate, w.tile, w.counts, w.perm, w.pos_of, w.tile_expert, w.max_tiles};
-        MX(mx::moe_route(st, dt, mp, lc));
-        if (mo.experts && w.sorted) {  // grouped products: sorted rows of h -> act(gate) * up -> down, expert e at row e * N of the stacked weights
-          const int rows = w.max_tiles * w.tile;
-          MX(mx::moe_gather(st, dt, w.h, w.perm, w.sorted, rows, H, mo.top, lc));
-          TcExtra xg;
-          xg.tile_group = w.tile_expert;
-          xg.n_groups = mo.experts;
-          RC((listed_gemm_tc<T, TCE_SWIGLU>(c, w.sorted, b->m_eg, nullptr, w.act, rows, 2 * mo.ff, H, mo.act, mo.ff, 0.f, xg)));
-          RC((listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, w.act, b->m_ed, nullptr, w.y, rows, H, mo.ff, 0, 0, 0.f, xg)));
-        } else if (mo.experts) {
-          mx::MoeExperts me{w.h, b->m_eg, b->m_ed, w.act, w.y, M, H, mo.ff, mo.top, mo.act, w.perm, w.tile_expert, w.tile, w.max_tiles};
-          MX(mx::moe_experts(st, dt, me, lc));
-        }
-        mx::MoeCombine mc{cur, x_out, w.h, w.y, w.wts, w.ids, w.pos_of, M, H, mo.top, mo.experts};
-        MX(mx::moe_combine(st, dt, mc, lc));
-        if (mo.shared_ff) {
-          RowsGemm gu{w.h, b->wgu, nullptr, w.sact, M, 2 * mo.shared_ff, H, H, mo.shared_ff, mo.act, 0.f};
-          if (listed_tc<T>(c, M, 2 * mo.shared_ff, H)) RC((listed_gemm_tc<T, TCE_SWIGLU>(c, w.h, b->wgu, nullptr, w.sact, M, 2 * mo.shared_ff, H, mo.act, mo.shared_ff)));
-          else RC((gemm_rows_T<T, RE_GATE_UP>(c, gu)));
-          RowsGemm gd{w.sact, b->wd, x_out, x_out, M, H, mo.shared_ff, mo.shared_ff, H, 0, 0.f, w.sgate};
-          if (listed_tc<T>(c, M, H, mo.shared_ff) && ((uintptr_t)x_out & 15) == 0) {
-            TcExtra xs;
-            xs.row_scale = w.sgate;
-            RC((listed_gemm_tc<T, TCE_RESIDUAL_F32>(c, w.sact, b->wd, x_out, x_out, M, H, mo.shared_ff, 0, 0, 0.f, xs)));
-          } else RC((gemm_rows_T<T, RE_RESIDUAL_F32>(c, gd)));
-        }
+        RC(enqueue_routed_ff<T>(c, b, w.moe, w.h, cur, x_out, M, lc));
       }
     }
     return CAKE_B200_OK;
@@ -2507,6 +2736,34 @@ extern "C" int cake_b200_stream_inject(cake_b200_ctx *c, float *x_dev, const flo
   RC(wait_loads(c));
   MX(mx::stream_inject(c->stream, c->cfg.dtype, x_dev, x0_dev, c->inject_vec[slot], rows, c->cfg.hidden, &c->launches));
   return CAKE_B200_OK;
+}
+
+extern "C" int cake_b200_stream_project(cake_b200_ctx *c, float *x_dev, const float *x0_dev, const void *w, int rows) {
+  if (!c || !x_dev || !x0_dev || !w || rows < 1) return fail(CAKE_B200_EINVAL, "bad stream_project arguments");
+  if (!c->cfg.layer_list) return fail(CAKE_B200_EINVAL, "stream_project is for models with an fp32 residual stream");
+  CU(cudaSetDevice(c->device));
+  const size_t H = c->cfg.hidden;
+  if (c->proj_src != w) {
+    if (c->proj_w) { CU(cudaStreamSynchronize(c->stream)); cudaFree(c->proj_w); c->proj_w = nullptr; }
+    RC(upload(c, &c->proj_w, w, H * 2 * H * c->es));
+    RC(pipe_mark(c));
+    c->proj_src = w;
+  }
+  RC(wait_loads(c));
+  const size_t need = (size_t)rows * 2 * H * c->es + 16;
+  if (need > c->proj_ws_cap) {
+    CU(cudaStreamSynchronize(c->stream));
+    if (c->proj_ws) cudaFree(c->proj_ws);
+    c->proj_ws = nullptr;
+    c->proj_ws_cap = 0;
+    CU(cudaMalloc(&c->proj_ws, need));
+    c->proj_ws_cap = need;
+  }
+  MX(mx::concat_rows(c->stream, c->cfg.dtype, x_dev, x0_dev, c->proj_ws, rows, (int)H, &c->launches));
+  return DISPATCH_T3(c->cfg.dtype, T_LAMBDA {
+    typedef typename decltype(tag_)::type T;
+    return gemm_f32_out<T>(c, c->proj_ws, c->proj_w, x_dev, rows, (int)H, 2 * (int)H);
+  });
 }
 
 // ------------------------------------------------------------------------------------------ forward_batch
@@ -2631,6 +2888,7 @@ extern "C" int cake_b200_embed(cake_b200_ctx *c, const uint32_t *ids_host, int b
     c->d_ids_cap = n;
   }
   CU(cudaMemcpyAsync(c->d_ids, ids_host, n * 4, cudaMemcpyHostToDevice, c->stream));
+  c->d_ids_n = n;
   // the ids buffer is pageable in general: the copy above returns after staging, safe to reuse
   if (c->cfg.layer_list)  // the fp32 residual stream starts here
     return DISPATCH_T3(c->cfg.dtype, T_LAMBDA {
@@ -2664,6 +2922,17 @@ extern "C" int cake_b200_head_load_tables(cake_b200_ctx *c, const cake_b200_embe
     c->pos_rows = t->pos_rows;
   }
   c->final_norm_offset = t->final_norm_offset;
+  if (t->side) {
+    if (t->side_cols < 1) return fail(CAKE_B200_EINVAL, "bad side table size");
+    RC(upload(c, &c->side_tab, t->side, (size_t)c->cfg.vocab * t->side_cols * c->es));
+    c->side_cols = t->side_cols;
+  }
+  if (t->final_norm_kind == 1) {
+    if (!t->final_bias || c->cfg.scalar_final_norm) return fail(CAKE_B200_EINVAL, "the squashing final norm needs its offset vector and a vector gain");
+    RC(upload(c, &c->ln_f_b, t->final_bias, H * c->es));
+    c->final_norm_kind = 1;
+    c->final_alpha = t->final_alpha;
+  } else if (t->final_norm_kind != 0) return fail(CAKE_B200_EINVAL, "final_norm_kind %d", t->final_norm_kind);
   return pipe_mark(c);
 }
 
@@ -2688,6 +2957,7 @@ extern "C" int cake_b200_embed_at(cake_b200_ctx *c, cake_b200_cache *kc, const u
   }
   CU(cudaMemcpyAsync(c->d_ids, ids_host, n * 4, cudaMemcpyHostToDevice, c->stream));
   CU(cudaMemcpyAsync(c->d_ids + n, kc->last_tok.data(), (size_t)batch * 4, cudaMemcpyHostToDevice, c->stream));
+  c->d_ids_n = n;
   CU(cudaStreamSynchronize(c->stream));  // both sources are pageable host memory that changes below / belongs to the caller
   mx::EmbedTables et{c->embed, c->d_ids, c->bigram, c->pos_tab, (float *)x_dev, batch, seq, c->cfg.hidden, c->cfg.vocab, c->bigram_rows - 1,
                      c->mul_prev, c->mul_cur, index_pos, c->cfg.embed_scale};
@@ -2718,6 +2988,11 @@ static int listed_logits(cake_b200_ctx *c, const void *x_dev, const int *rows_ho
   }
   return DISPATCH_T3(c->cfg.dtype, T_LAMBDA {
     typedef typename decltype(tag_)::type T;
+    if (c->final_norm_kind == 1) {
+      mx::TanhNorm fn{(const float *)x_dev, rows_host ? c->sp_rows_idx : nullptr, row_mul, row_add, c->ln_f, c->ln_f_b, c->final_alpha, nullptr, nullptr,
+                      c->sp_hn, n, (int)H};
+      MX(mx::tanh_norm(c->stream, c->cfg.dtype, fn, &c->launches));
+    } else
     RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(n), dim3(256), 0, (const float *)x_dev, (const int *)(rows_host ? c->sp_rows_idx : nullptr),
                   row_mul, row_add, (const T *)c->ln_f,
                   c->cfg.scalar_final_norm ? 0 : 1, (const T *)nullptr, (const float *)nullptr, (float *)nullptr, (T *)c->sp_hn, (T *)nullptr, 1,

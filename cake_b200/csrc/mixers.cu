@@ -900,7 +900,10 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const MoePlan p) {
   const T *corr = reinterpret_cast<const T *>(p.correction);
   float z[MOE_MAX_SLOTS];
 #pragma unroll
-  for (int sI = 0; sI < MOE_MAX_SLOTS; sI++) z[sI] = lane + 32 * sI < E ? lg[lane + 32 * sI] : -INFINITY;
+  for (int sI = 0; sI < MOE_MAX_SLOTS; sI++) {
+    z[sI] = lane + 32 * sI < E ? lg[lane + 32 * sI] : -INFINITY;
+    if (p.logit_bias && lane + 32 * sI < E) z[sI] += DT<T>::to_f(corr[lane + 32 * sI]);
+  }
   float mx = -INFINITY;
 #pragma unroll
   for (int sI = 0; sI < MOE_MAX_SLOTS; sI++) mx = fmaxf(mx, z[sI]);
@@ -915,6 +918,10 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const MoePlan p) {
 #pragma unroll
   for (int sI = 0; sI < MOE_MAX_SLOTS; sI++) {
     const int e = lane + 32 * sI;
+    if (p.logit_bias) {  // the choice is by the logits themselves; exp(z - max) / (sum over the chosen) is their softmax
+      ch[sI] = z[sI];
+      continue;
+    }
     sc[sI] = sc[sI] / sum;
     ch[sI] = e < E ? sc[sI] + DT<T>::to_f(corr[e]) : -INFINITY;
   }
@@ -1122,6 +1129,10 @@ __global__ void __launch_bounds__(256) moe_expert_kernel(const MoeExperts p) {
       const int n = n0 + tx * 4 + j;
       if (n >= N) continue;
       if (PHASE == 0) {
+        if (p.act_kind == 2) {
+          reinterpret_cast<T *>(p.act)[(size_t)(row0 + r) * p.ff + n] = DT<T>::from_f(gated_pair<T>(acc[i][j], acu[i][j], 2, p.limit));
+          continue;
+        }
         const float g = rnd<T>(act_f(rnd<T>(acc[i][j]), p.act_kind));
         reinterpret_cast<T *>(p.act)[(size_t)(row0 + r) * p.ff + n] = DT<T>::from_f(g * rnd<T>(acu[i][j]));
       } else {
@@ -1144,10 +1155,10 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombine p) {
   const int m = blockIdx.x;
   const T *h = reinterpret_cast<const T *>(p.h) + (size_t)m * p.W;
   if ((p.W & 3) == 0) {  // 16-byte loads and stores of the fp32 rows
-    const float4 *x4 = reinterpret_cast<const float4 *>(p.x + (size_t)m * p.W);
+    const float4 *x4 = p.x ? reinterpret_cast<const float4 *>(p.x + (size_t)m * p.W) : nullptr;
     float4 *o4 = reinterpret_cast<float4 *>(p.x_out + (size_t)m * p.W);
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < p.W / 4; i += gridDim.y * blockDim.x) {
-      float4 s = x4[i];
+      float4 s = x4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
       for (int k = 0; k < p.top; k++) {
         const size_t pr = (size_t)m * p.top + k;
         const float w = p.wts[pr];
@@ -1170,7 +1181,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombine p) {
       const int e = p.ids[pr];
       s = fmaf(p.wts[pr], e < p.experts ? p.y[(size_t)p.pos_of[pr] * p.W + i] : DT<T>::to_f(h[i]), s);
     }
-    p.x_out[(size_t)m * p.W + i] = p.x[(size_t)m * p.W + i] + s;
+    p.x_out[(size_t)m * p.W + i] = (p.x ? p.x[(size_t)m * p.W + i] : 0.f) + s;
   }
 }
 int moe_combine(cudaStream_t st, int dtype, const MoeCombine &p, uint64_t *launches) {

@@ -147,6 +147,9 @@ struct MoePlan {
   int *pos_of;           // [M * top]: m * top + slot -> sorted row (pairs of identity experts: untouched)
   int *tile_expert;      // [max_tiles]: the expert of a block of `tile` sorted rows, or -1 (unused block)
   int max_tiles;
+  // 1: `correction` is a bias of the logits (z = Wr h + correction); the `top` largest z are chosen and their weights are the
+  // softmax over the chosen z alone (times scale)
+  int logit_bias = 0;
 };
 int moe_route(cudaStream_t, int dtype, const MoePlan &, uint64_t *launches);
 
@@ -163,10 +166,12 @@ struct MoeExperts {
   int M, W, ff, top, act_kind;
   const int *perm, *tile_expert;
   int tile, max_tiles;
+  float limit = 0.f;     // act_kind 2 (the clamped form): its limit
 };
 int moe_experts(cudaStream_t, int dtype, const MoeExperts &, uint64_t *launches);
 
 // x_out[m] = x[m] + sum over slots of wts * (expert: y[pos_of[m * top + slot]]; identity: h[m]), slots in order
+// (x == nullptr: the sum alone)
 struct MoeCombine {
   const float *x;
   float *x_out;
@@ -324,6 +329,93 @@ int embed_tables(cudaStream_t, int dtype, const EmbedTables &, uint64_t *launche
 
 // ---- x[m] += (x0 ? x0[m] : 0) + vec   (fp32 stream; vec [W] in D) --------------------------------------------------------
 int stream_inject(cudaStream_t, int dtype, float *x, const float *x0, const void *vec, int M, int W, uint64_t *launches);
+
+// ---- element-wise squashing norm: out = tanh(alpha * y) * w + b  (no statistics of the row) ---------------------------------
+// Output row i reads input row rows[i] (rows != nullptr) or i * row_mul + row_add.  With x the result is added to it:
+// out32 = x + norm(y) (the sublayer's way back into the residual stream; out32 may alias x).
+struct TanhNorm {
+  const float *y;        // [*, n] fp32
+  const int *rows;
+  int row_mul, row_add;
+  const void *w, *b;     // [n] D
+  float alpha;
+  const float *x;        // [M, n] fp32 or nullptr
+  float *out32;          // one of the two outputs: [M, n] fp32 ...
+  void *outD;            // ... or [M, n] D
+  int M, n;
+};
+int tanh_norm(cudaStream_t, int dtype, const TanhNorm &, uint64_t *launches);
+
+// ---- RMS norm with a plain gain over a column range of rows in D (a low-rank latent) ------------------------------------------
+// Row m = (b, t) of a step of S tokens lands in output row b * out_rows + out_row0 + t: a scratch buffer (out_rows = S,
+// out_row0 = 0) or a cache of `cap` positions per batch row (out_rows = cap, out_row0 = the step's first position).
+struct RmsCols {
+  const void *in;        // [M, ld] D, n entries from column col
+  int ld, col;
+  const void *w;         // [n] D
+  void *out;             // [*, ldo] D
+  int ldo, out_rows, out_row0;
+  int M, S, n;
+  float eps;
+};
+int rms_cols(cudaStream_t, int dtype, const RmsCols &, uint64_t *launches);
+
+// ---- queries and keys of a step: rotation of the leading entries of every head, unit RMS per head, keys and values appended ----
+// q_h <- rot(q_h), k_g <- rot(k_g) on the first rope_dims entries (pairs i, i + rope_dims / 2; table row = position), then with
+// unit_norm x / sqrt(mean(x^2) + eps) over the head; q leaves in D, k and v join the caches at positions pos0 ..
+struct QkPrep {
+  const void *proj;      // [M, ld] D
+  int ld, q_col, k_col, v_col;
+  const float *cos_t, *sin_t;   // [positions, rope_dims / 2] or nullptr
+  int rope_dims, unit_norm;
+  float eps;
+  void *q_out;           // [M, heads * dim] D
+  void *kc, *vc;         // [B, kv_heads, cap, dim], [B, kv_heads, cap, vdim] D
+  int B, S, heads, kv_heads, dim, vdim, cap, pos0;
+};
+int qk_prep(cudaStream_t, int dtype, const QkPrep &, uint64_t *launches);
+
+// ---- softmax attention over cached keys and values with a sliding window, kept first tokens and a sink -----------------------
+// Row i (absolute position) of head h sees key j of key head h / (heads / kv_heads) when j <= i and (window == 0 or i - j < window
+// or j < keep_first).  s = (q . k_j) * scale; w_j = exp(s_j) / (sum over visible exp(s) + (sink ? exp(sink[h]) : 0)); the sink has
+// no value.  out_h = (sum_j w_j v_j) * sigmoid(gate) with one gate per entry (gate_per_head 0: column h * vdim + e) or per head
+// (gate_per_head 1: column h).  Keys and values may be the same rows (a shared latent: kv_heads 1, vc == kc, vdim == dim).
+struct WindowAttn {
+  const void *q;         // [M, ldq] D, head h at column h * dim
+  int ldq;
+  const void *kc, *vc;   // [B, kv_heads, cap, dim], [B, kv_heads, cap, vdim] D
+  const void *gate;      // [M, ldg] D or nullptr
+  int ldg, gate_per_head;
+  const void *sink;      // [heads] D or nullptr
+  void *out;             // [M, ldo] D, head h at column h * vdim
+  int ldo;
+  int B, S, heads, kv_heads, dim, vdim, cap, pos0, window, keep_first;
+  float scale;
+  // steps of a few rows over many keys: the visible keys of a (row, head) are split over nsplit CTAs whose partial (max, sum,
+  // weighted values) land in part [M * heads, nsplit, vdim + 2] fp32 and are merged by a second kernel
+  float *part = nullptr;
+  int nsplit = 0;
+};
+int window_attention(cudaStream_t, int dtype, const WindowAttn &, uint64_t *launches);
+// The tiled form for portions in 16-bit D (tensor-core products, a CTA per 64 rows of a head): true when the shapes fit it.
+bool window_attention_tiled_ok(int dtype, const WindowAttn &);
+int window_attention_tiled(cudaStream_t, int dtype, const WindowAttn &, uint64_t *launches);
+
+// ---- per-layer token input: x += rms(P (gelu_tanh(G x) * e)) * w,  e = table[id, col .. col + dim) ----------------------------
+struct TokenSide {
+  const float *x;        // [M, W] fp32
+  float *x_out;          // may alias x
+  const uint32_t *ids;   // [M]
+  const void *table;     // [vocab, table_ld] D
+  int table_ld, col;
+  const void *gate, *proj, *norm;   // [dim, W], [W, dim], [W] D
+  int M, W, dim;
+  float eps;
+};
+int token_side(cudaStream_t, int dtype, const TokenSide &, uint64_t *launches);
+
+// ---- out[m] = [x[m] | x0[m]] in D  (the operand of a projection of the stream and the embedding output back into the stream) --
+int concat_rows(cudaStream_t, int dtype, const float *x, const float *x0, void *out, int M, int W, uint64_t *launches);
 
 }  // namespace mx
 }  // namespace cake

@@ -1,0 +1,369 @@
+// mixers_window.cu — kernels behind the second half of mixers.cuh: the element-wise squashing norm, RMS norms of column ranges
+// (low-rank latents), rotation + unit norm of queries and keys with the cache append, softmax attention over cached keys and
+// values with a sliding window, kept first tokens and a sink (per-row form with split keys for short steps, and a tiled
+// tensor-core form for portions in 16-bit D), the per-layer token input and the stream / embedding concatenation.
+// sm_100a only.  fp32 everywhere the interface says so; D only where a projection, a cache row or a weight is stored.
+#include "mixers.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace cake {
+namespace mx {
+
+#define MX_DISPATCH(dtype, ...)                               \
+  do {                                                        \
+    if ((dtype) == 2) { typedef float T; __VA_ARGS__; }       \
+    else if ((dtype) == 1) { typedef __half T; __VA_ARGS__; } \
+    else { typedef __nv_bfloat16 T; __VA_ARGS__; }            \
+  } while (0)
+#define MX_DONE(n)                     \
+  do {                                 \
+    if (launches) *launches += (n);    \
+    return (int)cudaGetLastError();    \
+  } while (0)
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ---------------------------------------------------------------------------------------------- squashing norm
+template <typename T>
+__global__ void __launch_bounds__(256) tanh_norm_kernel(const TanhNorm p) {
+  const int m = blockIdx.x;
+  const size_t src = p.rows ? (size_t)p.rows[m] : (size_t)m * p.row_mul + p.row_add;
+  const float *y = p.y + src * p.n;
+  const float *x = p.x ? p.x + (size_t)m * p.n : nullptr;
+  const T *w = reinterpret_cast<const T *>(p.w), *b = reinterpret_cast<const T *>(p.b);
+  if ((p.n & 3) == 0) {  // 16-byte loads of the fp32 rows
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < p.n / 4; i += gridDim.y * blockDim.x) {
+      const float4 v = reinterpret_cast<const float4 *>(y)[i];
+      float r[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; e++) r[e] = fmaf(tanhf(p.alpha * r[e]), DT<T>::to_f(w[4 * i + e]), DT<T>::to_f(b[4 * i + e]));
+      if (p.out32) {
+        if (x) {
+          const float4 xv = reinterpret_cast<const float4 *>(x)[i];
+          r[0] += xv.x; r[1] += xv.y; r[2] += xv.z; r[3] += xv.w;
+        }
+        reinterpret_cast<float4 *>(p.out32 + (size_t)m * p.n)[i] = make_float4(r[0], r[1], r[2], r[3]);
+      } else {
+        T *o = reinterpret_cast<T *>(p.outD) + (size_t)m * p.n + 4 * i;
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[e] = DT<T>::from_f(r[e]);
+      }
+    }
+    return;
+  }
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < p.n; i += gridDim.y * blockDim.x) {
+    float r = fmaf(tanhf(p.alpha * y[i]), DT<T>::to_f(w[i]), DT<T>::to_f(b[i]));
+    if (p.out32) p.out32[(size_t)m * p.n + i] = x ? x[i] + r : r;
+    else reinterpret_cast<T *>(p.outD)[(size_t)m * p.n + i] = DT<T>::from_f(r);
+  }
+}
+int tanh_norm(cudaStream_t st, int dtype, const TanhNorm &p, uint64_t *launches) {
+  if (p.M < 1 || p.n < 1 || !p.y || !p.w || !p.b || (!p.out32 && !p.outD)) return (int)cudaErrorInvalidValue;
+  const int per = (p.n + 1023) / 1024;  // few rows: several CTAs per row
+  MX_DISPATCH(dtype, (tanh_norm_kernel<T><<<dim3(p.M, p.M < 256 ? per : 1), 256, 0, st>>>(p)));
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- RMS norm of a column range
+template <typename T>
+__global__ void __launch_bounds__(128) rms_cols_kernel(const RmsCols p) {
+  __shared__ float red[4];
+  const int m = blockIdx.x, b = m / p.S, t = m % p.S;
+  const T *in = reinterpret_cast<const T *>(p.in) + (size_t)m * p.ld + p.col;
+  const T *w = reinterpret_cast<const T *>(p.w);
+  T *out = reinterpret_cast<T *>(p.out) + ((size_t)b * p.out_rows + p.out_row0 + t) * p.ldo;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
+    const float v = DT<T>::to_f(in[i]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  const float inv = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)p.n + p.eps);
+  for (int i = threadIdx.x; i < p.n; i += blockDim.x) out[i] = DT<T>::from_f(DT<T>::to_f(in[i]) * inv * DT<T>::to_f(w[i]));
+}
+int rms_cols(cudaStream_t st, int dtype, const RmsCols &p, uint64_t *launches) {
+  if (p.M < 1 || p.n < 1 || p.S < 1) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, (rms_cols_kernel<T><<<p.M, 128, 0, st>>>(p)));
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- rotation, unit norm, append
+// entry i of a head whose first `dims` entries are paired (i, i + dims / 2); cs / sn: this position's table row
+template <typename T>
+__device__ __forceinline__ float rotated_entry(const T *v, int i, int dims, const float *cs, const float *sn) {
+  const int half = dims >> 1;
+  if (i >= dims) return DT<T>::to_f(v[i]);
+  if (i < half) return DT<T>::to_f(v[i]) * cs[i] - DT<T>::to_f(v[i + half]) * sn[i];
+  return DT<T>::to_f(v[i]) * cs[i - half] + DT<T>::to_f(v[i - half]) * sn[i - half];
+}
+template <typename T>
+__global__ void __launch_bounds__(128) qk_prep_kernel(const QkPrep p) {
+  const int m = blockIdx.x, b = m / p.S, t = m % p.S, pos = p.pos0 + t;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const T *row = reinterpret_cast<const T *>(p.proj) + (size_t)m * p.ld;
+  const int dims = p.cos_t ? p.rope_dims : 0, half = dims >> 1;
+  const float *cs = p.cos_t ? p.cos_t + (size_t)pos * half : nullptr, *sn = p.sin_t ? p.sin_t + (size_t)pos * half : nullptr;
+  for (int hv = warp; hv < p.heads + p.kv_heads; hv += nw) {
+    const bool is_q = hv < p.heads;
+    const int g = hv - p.heads;
+    const T *v = is_q ? row + p.q_col + (size_t)hv * p.dim : row + p.k_col + (size_t)g * p.dim;
+    T *o = is_q ? reinterpret_cast<T *>(p.q_out) + ((size_t)m * p.heads + hv) * p.dim
+                : reinterpret_cast<T *>(p.kc) + (((size_t)b * p.kv_heads + g) * p.cap + pos) * p.dim;
+    float inv = 1.f;
+    if (p.unit_norm) {
+      float ss = 0.f;
+      for (int i = lane; i < p.dim; i += 32) {
+        const float r = rotated_entry<T>(v, i, dims, cs, sn);
+        ss = fmaf(r, r, ss);
+      }
+      ss = warp_sum(ss);
+      inv = 1.0f / sqrtf(ss / (float)p.dim + p.eps);
+    }
+    for (int i = lane; i < p.dim; i += 32) o[i] = DT<T>::from_f(rotated_entry<T>(v, i, dims, cs, sn) * inv);
+  }
+  for (int i = threadIdx.x; i < p.kv_heads * p.vdim; i += blockDim.x) {
+    const int g = i / p.vdim, e = i % p.vdim;
+    reinterpret_cast<T *>(p.vc)[(((size_t)b * p.kv_heads + g) * p.cap + pos) * p.vdim + e] = row[p.v_col + i];
+  }
+}
+int qk_prep(cudaStream_t st, int dtype, const QkPrep &p, uint64_t *launches) {
+  if (p.B < 1 || p.S < 1 || p.heads < 1 || p.kv_heads < 1 || (p.cos_t && (p.rope_dims & 1 || p.rope_dims > p.dim))) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, (qk_prep_kernel<T><<<p.B * p.S, 128, 0, st>>>(p)));
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- window attention, per row
+// CTA (row-head, split): the visible keys are the kept first tokens that have left the window, then the window; the CTA's
+// four warps walk its share four keys at a time each (lanes split the columns of a key and of a value row), their running
+// softmax states are merged in shared memory.  Without splits the CTA adds the sink, normalises, gates and writes the output;
+// with splits it leaves (max, sum, weighted values) for the merge kernel.
+template <typename T, int NR>
+__global__ void __launch_bounds__(128) window_attn_kernel(const WindowAttn p) {
+  __shared__ float sm_m[4], sm_l[4];
+  extern __shared__ float sm_acc[];  // [4][vdim]
+  const int mh = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = mh / p.heads, h = mh % p.heads, b = m / p.S, t = m % p.S, pos = p.pos0 + t;
+  const int g = h / (p.heads / p.kv_heads);
+  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int nA = min(p.keep_first, lo), total = nA + pos - lo + 1;
+  const int nsplit = p.nsplit > 1 ? p.nsplit : 1;
+  const int per = nsplit > 1 ? ((total + nsplit - 1) / nsplit + 15) / 16 * 16 : total;
+  const int k0 = split * per, k1 = min(total, k0 + per);
+  const T *q = reinterpret_cast<const T *>(p.q) + (size_t)m * p.ldq + (size_t)h * p.dim;
+  const T *kc = reinterpret_cast<const T *>(p.kc) + ((size_t)b * p.kv_heads + g) * p.cap * p.dim;
+  const T *vc = reinterpret_cast<const T *>(p.vc) + ((size_t)b * p.kv_heads + g) * p.cap * p.vdim;
+  const bool shared_rows = p.kc == p.vc && p.dim == p.vdim;  // a key row is also the value row
+  float qv[NR], acc[NR];
+#pragma unroll
+  for (int i = 0; i < NR; i++) {
+    const int c = lane + 32 * i;
+    qv[i] = c < p.dim ? DT<T>::to_f(q[c]) * p.scale : 0.f;
+    acc[i] = 0.f;
+  }
+  float mx = -INFINITY, l = 0.f;
+  for (int jj = k0 + 4 * warp; jj < k1; jj += 16) {
+    float vv[4][NR], s[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const int ju = jj + u < k1 ? jj + u : jj;
+      const int j = ju < nA ? ju : lo + ju - nA;
+      const T *krow = kc + (size_t)j * p.dim;
+      float part = 0.f;
+      if (shared_rows) {
+#pragma unroll
+        for (int i = 0; i < NR; i++) {
+          const int c = lane + 32 * i;
+          vv[u][i] = c < p.dim ? DT<T>::to_f(krow[c]) : 0.f;
+          part = fmaf(qv[i], vv[u][i], part);
+        }
+      } else {
+        const T *vrow = vc + (size_t)j * p.vdim;
+#pragma unroll
+        for (int i = 0; i < NR; i++) {
+          const int c = lane + 32 * i;
+          part = fmaf(qv[i], c < p.dim ? DT<T>::to_f(krow[c]) : 0.f, part);
+          vv[u][i] = c < p.vdim ? DT<T>::to_f(vrow[c]) : 0.f;
+        }
+      }
+      s[u] = part;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      s[u] = warp_sum(s[u]);
+      if (jj + u >= k1) s[u] = -INFINITY;
+    }
+    const float mn = fmaxf(fmaxf(mx, fmaxf(s[0], s[1])), fmaxf(s[2], s[3]));
+    const float corr = expf(mx - mn);  // first round: exp(-inf) = 0
+    float pr[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) pr[u] = expf(s[u] - mn);
+    l = l * corr + ((pr[0] + pr[1]) + (pr[2] + pr[3]));
+#pragma unroll
+    for (int i = 0; i < NR; i++) {
+      float a = acc[i] * corr;
+#pragma unroll
+      for (int u = 0; u < 4; u++) a = fmaf(pr[u], vv[u][i], a);
+      acc[i] = a;
+    }
+    mx = mn;
+  }
+  if (lane == 0) { sm_m[warp] = mx; sm_l[warp] = l; }
+#pragma unroll
+  for (int i = 0; i < NR; i++) {
+    const int c = lane + 32 * i;
+    if (c < p.vdim) sm_acc[warp * p.vdim + c] = acc[i];
+  }
+  __syncthreads();
+  float M4 = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+  float f[4], L = 0.f;
+  if (nsplit > 1) {
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      f[w] = sm_m[w] == -INFINITY ? 0.f : expf(sm_m[w] - M4);
+      L = fmaf(sm_l[w], f[w], L);
+    }
+    float *out = p.part + ((size_t)mh * nsplit + split) * (p.vdim + 2);
+    if (threadIdx.x == 0) { out[0] = M4; out[1] = L; }
+    for (int c = threadIdx.x; c < p.vdim; c += blockDim.x)
+      out[2 + c] = (sm_acc[c] * f[0] + sm_acc[p.vdim + c] * f[1]) + (sm_acc[2 * p.vdim + c] * f[2] + sm_acc[3 * p.vdim + c] * f[3]);
+    return;
+  }
+  float sink_term = 0.f;
+  if (p.sink) {
+    const float sk = DT<T>::to_f(reinterpret_cast<const T *>(p.sink)[h]);
+    M4 = fmaxf(M4, sk);
+    sink_term = expf(sk - M4);
+  }
+#pragma unroll
+  for (int w = 0; w < 4; w++) {
+    f[w] = sm_m[w] == -INFINITY ? 0.f : expf(sm_m[w] - M4);
+    L = fmaf(sm_l[w], f[w], L);
+  }
+  const float il = 1.0f / (L + sink_term);
+  const T *gate = reinterpret_cast<const T *>(p.gate);
+  const float gh = gate && p.gate_per_head ? sigmoid_f(DT<T>::to_f(gate[(size_t)m * p.ldg + h])) : 1.f;
+  T *out = reinterpret_cast<T *>(p.out) + (size_t)m * p.ldo + (size_t)h * p.vdim;
+  for (int c = threadIdx.x; c < p.vdim; c += blockDim.x) {
+    float o = ((sm_acc[c] * f[0] + sm_acc[p.vdim + c] * f[1]) + (sm_acc[2 * p.vdim + c] * f[2] + sm_acc[3 * p.vdim + c] * f[3])) * il;
+    if (gate) o *= p.gate_per_head ? gh : sigmoid_f(DT<T>::to_f(gate[(size_t)m * p.ldg + (size_t)h * p.vdim + c]));
+    out[c] = DT<T>::from_f(o);
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(128) window_attn_merge_kernel(const WindowAttn p) {
+  const int mh = blockIdx.x, m = mh / p.heads, h = mh % p.heads, stride = p.vdim + 2;
+  const float *part = p.part + (size_t)mh * p.nsplit * stride;
+  float M = p.sink ? DT<T>::to_f(reinterpret_cast<const T *>(p.sink)[h]) : -INFINITY;
+  float L = p.sink ? 1.f : 0.f;  // the sink's term relative to its own logit; rescaled below
+  const float sk = M;
+  for (int s = 0; s < p.nsplit; s++) M = fmaxf(M, part[(size_t)s * stride]);
+  L = p.sink ? expf(sk - M) : 0.f;
+  for (int s = 0; s < p.nsplit; s++) {
+    const float ms = part[(size_t)s * stride];
+    if (ms != -INFINITY) L = fmaf(part[(size_t)s * stride + 1], expf(ms - M), L);
+  }
+  const T *gate = reinterpret_cast<const T *>(p.gate);
+  const float gh = gate && p.gate_per_head ? sigmoid_f(DT<T>::to_f(gate[(size_t)m * p.ldg + h])) : 1.f;
+  T *out = reinterpret_cast<T *>(p.out) + (size_t)m * p.ldo + (size_t)h * p.vdim;
+  for (int c = threadIdx.x; c < p.vdim; c += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < p.nsplit; s++) {
+      const float ms = part[(size_t)s * stride];
+      if (ms != -INFINITY) a = fmaf(part[(size_t)s * stride + 2 + c], expf(ms - M), a);
+    }
+    float o = a / L;
+    if (gate) o *= p.gate_per_head ? gh : sigmoid_f(DT<T>::to_f(gate[(size_t)m * p.ldg + (size_t)h * p.vdim + c]));
+    out[c] = DT<T>::from_f(o);
+  }
+}
+int window_attention(cudaStream_t st, int dtype, const WindowAttn &p, uint64_t *launches) {
+  const int D = p.dim > p.vdim ? p.dim : p.vdim;
+  if (D > 32 * 24 || p.heads < 1 || p.kv_heads < 1 || p.heads % p.kv_heads || p.window < 0 || p.keep_first < 0) return (int)cudaErrorInvalidValue;
+  const bool split = p.part && p.nsplit > 1;
+  const dim3 grid((unsigned)(p.B * p.S * p.heads), (unsigned)(split ? p.nsplit : 1));
+  const size_t smem = (size_t)4 * p.vdim * sizeof(float);
+  MX_DISPATCH(dtype, {
+    if (D <= 32 * 2) window_attn_kernel<T, 2><<<grid, 128, smem, st>>>(p);
+    else if (D <= 32 * 4) window_attn_kernel<T, 4><<<grid, 128, smem, st>>>(p);
+    else if (D <= 32 * 8) window_attn_kernel<T, 8><<<grid, 128, smem, st>>>(p);
+    else if (D <= 32 * 16) window_attn_kernel<T, 16><<<grid, 128, smem, st>>>(p);
+    else window_attn_kernel<T, 24><<<grid, 128, smem, st>>>(p);
+    if (split) window_attn_merge_kernel<T><<<grid.x, 128, 0, st>>>(p);
+  });
+  MX_DONE(split ? 2 : 1);
+}
+
+bool window_attention_tiled_ok(int, const WindowAttn &) { return false; }
+int window_attention_tiled(cudaStream_t, int, const WindowAttn &, uint64_t *) { return (int)cudaErrorInvalidValue; }
+
+// ---------------------------------------------------------------------------------------------- per-layer token input
+template <typename T>
+__global__ void __launch_bounds__(256) token_side_kernel(const TokenSide p) {
+  extern __shared__ float sm[];  // g [dim], y [W]
+  __shared__ float red[8];
+  float *gs = sm, *ys = sm + p.dim;
+  const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float *x = p.x + (size_t)m * p.W;
+  const T *e = reinterpret_cast<const T *>(p.table) + (size_t)p.ids[m] * p.table_ld + p.col;
+  const T *G = reinterpret_cast<const T *>(p.gate), *P = reinterpret_cast<const T *>(p.proj), *nw = reinterpret_cast<const T *>(p.norm);
+  for (int j = warp; j < p.dim; j += 8) {
+    const T *gr = G + (size_t)j * p.W;
+    float d = 0.f;
+    for (int i = lane; i < p.W; i += 32) d = fmaf(DT<T>::to_f(gr[i]), x[i], d);
+    d = warp_sum(d);
+    if (lane == 0) gs[j] = 0.5f * d * (1.0f + tanhf(0.7978845608028654f * (d + 0.044715f * d * d * d))) * DT<T>::to_f(e[j]);
+  }
+  __syncthreads();
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < p.W; i += blockDim.x) {
+    const T *pr = P + (size_t)i * p.dim;
+    float y = 0.f;
+    for (int j = 0; j < p.dim; j++) y = fmaf(DT<T>::to_f(pr[j]), gs[j], y);
+    ys[i] = y;
+    ss = fmaf(y, y, ss);
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < 8; w++) tot += red[w];
+  const float inv = 1.0f / sqrtf(tot / (float)p.W + p.eps);
+  for (int i = threadIdx.x; i < p.W; i += blockDim.x) p.x_out[(size_t)m * p.W + i] = x[i] + ys[i] * inv * DT<T>::to_f(nw[i]);
+}
+int token_side(cudaStream_t st, int dtype, const TokenSide &p, uint64_t *launches) {
+  const size_t smem = (size_t)(p.dim + p.W) * sizeof(float);
+  if (p.M < 1 || p.W < 1 || p.dim < 1 || smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(token_side_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    token_side_kernel<T><<<p.M, 256, smem, st>>>(p);
+  });
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- [x | x0] in D
+template <typename T>
+__global__ void __launch_bounds__(256) concat_rows_kernel(const float *__restrict__ x, const float *__restrict__ x0, T *__restrict__ out, int W) {
+  const size_t m = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    out[m * 2 * W + i] = DT<T>::from_f(x[m * W + i]);
+    out[m * 2 * W + W + i] = DT<T>::from_f(x0[m * W + i]);
+  }
+}
+int concat_rows(cudaStream_t st, int dtype, const float *x, const float *x0, void *out, int M, int W, uint64_t *launches) {
+  if (M < 1 || W < 1 || !x || !x0 || !out) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, (concat_rows_kernel<T><<<M, 256, 0, st>>>(x, x0, reinterpret_cast<T *>(out), W)));
+  MX_DONE(1);
+}
+
+}  // namespace mx
+}  // namespace cake

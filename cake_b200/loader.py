@@ -405,6 +405,57 @@ def nuvarax_block_tensors(vb, cfg: Config, index: int):
     return main, side
 
 
+def netolorn_block_tensors(vb, cfg: Config, index: int) -> Dict[str, object]:
+    """The tensors of layer ``index`` of a Netolorn checkpoint by the field names of ``cake_b200_mixer_tensors``, each checked
+    against the shape its MixerSpec declares.  Names under ``l<i>.``: ``norm1``, ``norm1b``, ``norm2``, ``norm2b`` (each with ``.b``
+    [width] and ``.alpha``, one number, which lands in the spec's ``norm_alpha``), ``side.{gate,proj,norm}`` and ``mix.*``: an
+    attention layer has ``q, k, v`` (+ ``.b``), ``sink``, ``g``, ``o``; a latent layer ``dq``, ``dq.norm``, ``uq``, ``dkv``, ``dkv.norm``,
+    ``uk``, ``uv``, ``g`` [heads, width], ``o``; ``mlp.{gate,up,down}`` (dense) or ``mlp.{router, router.b, e<j>.*, shared.*}``."""
+    sp, H, name = cfg.layers[index], cfg.hidden_size, cfg.layer_name(index)
+
+    def get(short, shape):
+        t = vb.get(f"{name}.{short}")
+        if t is None:
+            raise KeyError(f"tensor {name}.{short} not found")
+        if shape == () and t.numel() == 1:
+            t = t.reshape(())          # a single number may be stored as [] or [1]
+        if tuple(t.shape) != tuple(shape):
+            raise ValueError(f"shape mismatch for {name}.{short}, expected: {list(shape)}, got: {list(t.shape)}")
+        return t
+
+    has_ff = bool(sp.dense_ff or sp.moe is not None)
+    out: Dict[str, object] = {}
+    for k, (fld, fld_b, short) in enumerate((("norm1", "norm1_b", "norm1"), ("post1", "post1_b", "norm1b"), ("norm2", "norm2_b", "norm2"),
+                                             ("post2", "post2_b", "norm2b"))):
+        if k >= 2 and not has_ff:
+            continue
+        out[fld], out[fld_b] = get(short, (H,)), get(short + ".b", (H,))
+        sp.norm_alpha[k] = float(get(short + ".alpha", ()).to(torch.float32))
+    out["o"] = get("mix.o", (H, sp.inner))
+    if sp.type == "sink_attention":
+        sq, skv, svv = sp.heads * sp.dim, sp.n_kv * sp.dim, sp.n_kv * sp.vdim
+        out.update(q=get("mix.q", (sq, H)), q_b=get("mix.q.b", (sq,)), k=get("mix.k", (skv, H)), k_b=get("mix.k.b", (skv,)),
+                   v=get("mix.v", (svv, H)), v_b=get("mix.v.b", (svv,)), sink=get("mix.sink", (sp.heads,)), g=get("mix.g", (sp.inner, H)))
+    else:
+        out.update(dq=get("mix.dq", (sp.q_rank, H)), dq_norm=get("mix.dq.norm", (sp.q_rank,)), uq=get("mix.uq", (sp.heads * sp.dim, sp.q_rank)),
+                   dkv=get("mix.dkv", (sp.kv_rank, H)), dkv_norm=get("mix.dkv.norm", (sp.kv_rank,)), uk=get("mix.uk", (sp.heads * sp.dim, sp.kv_rank)),
+                   uv=get("mix.uv", (sp.inner, sp.kv_rank)), g=get("mix.g", (sp.heads, H)))
+    mo = sp.moe
+    if sp.dense_ff:
+        out.update(ff_gate=get("mlp.gate", (sp.dense_ff, H)), ff_up=get("mlp.up", (sp.dense_ff, H)), ff_down=get("mlp.down", (H, sp.dense_ff)))
+    elif mo is not None:
+        out.update(router=get("mlp.router", (mo.experts, H)), correction=get("mlp.router.b", (mo.experts,)),
+                   e_gate=[get(f"mlp.e{j}.gate", (mo.ff, H)) for j in range(mo.experts)],
+                   e_up=[get(f"mlp.e{j}.up", (mo.ff, H)) for j in range(mo.experts)],
+                   e_down=[get(f"mlp.e{j}.down", (H, mo.ff)) for j in range(mo.experts)])
+        if mo.shared_ff:
+            out.update(s_gate=get("mlp.shared.gate", (mo.shared_ff, H)), s_up=get("mlp.shared.up", (mo.shared_ff, H)),
+                       s_down=get("mlp.shared.down", (H, mo.shared_ff)), s_sg=get("mlp.shared.sg", (1, H)))
+    if sp.side_dim:
+        out.update(side_gate=get("side.gate", (sp.side_dim, H)), side_proj=get("side.proj", (H, sp.side_dim)), side_norm=get("side.norm", (H,)))
+    return out
+
+
 def detect_model_prefix(index_path: str, configured: str) -> str:
     """cake/mod.rs:335-357: the text before the first ``.layers.0.`` key of the index wins over the configured prefix."""
     if not os.path.exists(index_path):

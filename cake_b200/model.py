@@ -303,10 +303,10 @@ class MixerBlock(B200Transformer):
 def _mixer_struct(sp, views, ctx, keep):
     """(CMixerSpec, CMixerTensors) of one MixerSpec and its tensors (by field name; missing = NULL); device / host copies
     that must outlive the load call are appended to ``keep``."""
-    from .capi import CMixerSpec, CMixerTensors, CMoeSpec, CRotarySpec, MIXER_TENSOR_FIELDS
+    from .capi import CMixerSpec, CMixerTensors, CMoeSpec, CRotarySpec, MIXER_TENSOR_FIELDS, MIXER_TENSOR_FIELDS_2
     from .config import MIXER_KINDS
     args = {}
-    for fld in MIXER_TENSOR_FIELDS:
+    for fld in MIXER_TENSOR_FIELDS + MIXER_TENSOR_FIELDS_2:
         t = views.get(fld)
         if isinstance(t, list):
             ts = [x.to(ctx.torch_dtype).contiguous() for x in t]
@@ -326,9 +326,11 @@ def _mixer_struct(sp, views, ctx, keep):
     spec = CMixerSpec(MIXER_KINDS[sp.type], sp.heads, sp.dim, sp.vdim, sp.rot_dim, sp.kv_rank, sp.scale,
                       CRotarySpec(r.dims, r.base, r.factor, r.fast, r.slow, r.original),
                       decay if sp.decay else None, sp.state, sp.groups, sp.conv, sp.norm_groups,
-                      CMoeSpec(mo.experts, mo.identity, mo.top, mo.scale, mo.ff, mo.shared_ff, mo.act) if mo else CMoeSpec(),
+                      CMoeSpec(mo.experts, mo.identity, mo.top, mo.scale, mo.ff, mo.shared_ff, mo.act, mo.limit, mo.shared_limit, int(mo.logit_bias))
+                      if mo else CMoeSpec(),
                       sp.kv_heads, sp.bias_rows, sp.bias_max, sp.gate_cap, sp.norm_offset, sp.canon_taps, sp.dense_ff, sp.dense_act,
-                      sp.dense_limit, None)
+                      sp.dense_limit, None, sp.window, sp.keep_first, int(sp.qk_unit), sp.q_rank, sp.norm_kind, (ctypes.c_float * 4)(*sp.norm_alpha),
+                      sp.side_dim, sp.side_col)
     return spec, CMixerTensors(**args)
 
 
@@ -355,8 +357,27 @@ class SandwichBlock(MixerBlock):
         return cls(name, h, ctx)
 
 
+class SquashBlock(MixerBlock):
+    """A layer of a Netolorn model: a mixer-list block (``cake_b200_block_load_mixer``) with the squashing norm on both sides of
+    every sublayer, a per-layer token input behind the feed-forward, a dense or routed (clamped, logit-biased) feed-forward, and
+    sink attention or windowed latent attention as its mixer."""
+
+    @classmethod
+    def load(cls, name: str, ctx: Context) -> "SquashBlock":
+        from .loader import netolorn_block_tensors
+        cfg = ctx.config
+        index = [cfg.layer_name(i) for i in range(len(cfg.layers))].index(name)
+        sp = cfg.layers[index]
+        views = netolorn_block_tensors(ctx.var_builder, cfg, index)   # also fills sp.norm_alpha
+        keep = []
+        spec, tens = _mixer_struct(sp, views, ctx, keep)
+        h = c_void_p()
+        check(lib().cake_b200_block_load_mixer(ctx.h, index, byref(spec), byref(tens), byref(h)))
+        return cls(name, h, ctx)
+
+
 # Config.block_kind -> the Forwarder that loads and runs its layers
-BLOCK_CLASSES = {"nigenex": ListedBlock, "setodra": MixerBlock, "nuvarax": SandwichBlock}
+BLOCK_CLASSES = {"nigenex": ListedBlock, "setodra": MixerBlock, "nuvarax": SandwichBlock, "netolorn": SquashBlock}
 
 
 @dataclass
@@ -403,16 +424,21 @@ class TextModelBase:
         lnf = rms_norm_weight(get(n_norm, () if cfg.scalar_final_norm else (cfg.hidden_size,)), cfg)   # text_model.rs:186-192
         head = None if n_head is None else get(n_head, (cfg.vocab_size, cfg.hidden_size))
         check(lib().cake_b200_head_load(ctx.h, ptr(emb), ptr(lnf), ptr(head)))
-        tables = cfg.pair_embedding or cfg.learned_positions or cfg.final_norm_offset
-        if tables:   # embeddings that depend on a token's place in its sequence; the final norm's gain offset
+        tables = cfg.pair_embedding or cfg.learned_positions or cfg.final_norm_offset or cfg.token_side_dim or cfg.final_norm_kind
+        if tables:   # embeddings that depend on a token's place in its sequence; the final norm's gain offset or squashing form; the token inputs
             from .capi import CEmbedTables
             pe = cfg.pair_embedding
             big = get("bigram", (pe["buckets"] + 1, cfg.hidden_size)) if pe else None
             pos = vb["pos"].to(ctx.torch_dtype).contiguous() if cfg.learned_positions else None
             if pos is not None and (pos.dim() != 2 or pos.shape[1] != cfg.hidden_size):
                 raise ValueError(f"shape mismatch for pos, expected: [positions, {cfg.hidden_size}], got: {list(pos.shape)}")
+            side_cols = cfg.token_side_dim * len(cfg.layers)
+            side = get("side.embed", (cfg.vocab_size, side_cols)) if cfg.token_side_dim else None
+            fb = get(n_norm + ".b", (cfg.hidden_size,)) if cfg.final_norm_kind else None
+            fa = float(get(n_norm + ".alpha", ()).to(torch.float32)) if cfg.final_norm_kind else 0.0
             et = CEmbedTables(ptr(big), pe["buckets"] + 1 if pe else 0, pe["mul_prev"] if pe else 0, pe["mul_cur"] if pe else 0,
-                              ptr(pos), int(pos.shape[0]) if pos is not None else 0, float(cfg.final_norm_offset))
+                              ptr(pos), int(pos.shape[0]) if pos is not None else 0, float(cfg.final_norm_offset),
+                              ptr(side), side_cols, int(cfg.final_norm_kind), fa, ptr(fb))
             check(lib().cake_b200_head_load_tables(ctx.h, byref(et)))
         blocks: List[Forwarder] = []
         loaded: Dict[int, Forwarder] = {}   # a layer of a looped range appears once per pass and is loaded once
@@ -434,7 +460,10 @@ class TextModelBase:
         # run index -> pass number, for the runs in front of which the stream receives the pass's additions
         model.injections = {j: t for j, (_, t) in enumerate(plan) if t is not None} if cfg.loop_injects else {}
         model.embed_at = bool(cfg.pair_embedding or cfg.learned_positions)
-        if model.injections:
+        model.loop_in = None
+        if model.injections and cfg.loop_mode == "project":   # x <- W [x; x0] in front of every pass
+            model.loop_in = get("loop.in", (cfg.hidden_size, 2 * cfg.hidden_size))
+        elif model.injections:
             steps = get("loop.step", (int(cfg.loop["times"]), cfg.hidden_size))
             model.loop_steps = [steps[t].contiguous() for t in range(steps.shape[0])]
         return model
@@ -461,7 +490,10 @@ class TextModelBase:
         while i < n:
             if i in inject:  # a pass of a looped range starts: x += (embedding output, from the second pass on) + step vector
                 t = inject[i]
-                check(lib().cake_b200_stream_inject(ctx.h, ptr(x), ptr(x0) if t > 0 else None, ptr(self.loop_steps[t]), t, b * s))
+                if getattr(self, "loop_in", None) is not None:
+                    check(lib().cake_b200_stream_project(ctx.h, ptr(x), ptr(x0), ptr(self.loop_in), b * s))
+                else:
+                    check(lib().cake_b200_stream_inject(ctx.h, ptr(x), ptr(x0) if t > 0 else None, ptr(self.loop_steps[t]), t, b * s))
             ident = self.blocks[i].ident()
             j = i
             group = []

@@ -281,3 +281,62 @@ def make_nuvarax_checkpoint(cfg: Config, dtype: str = "bf16", seed: int = 1234, 
             sd[f"{b}.i"], sd[f"{b}.f"] = rn(r.heads, H, s=4 * std), rn(r.heads, H, s=4 * std)
             sd[f"{b}.i.b"], sd[f"{b}.f.b"] = rn(r.heads, s=0.5), ru(r.heads, lo=1.0, hi=4.0)
     return sd
+
+
+def make_netolorn_checkpoint(cfg: Config, dtype: str = "bf16", seed: int = 1234, device="cpu", std: float = 0.05, router_std: float = 0.5) -> dict:
+    """Random weights of a Netolorn model under the names its checkpoints use: ``embed``, ``head``, ``final.norm`` (+ ``.b``,
+    ``.alpha``), ``side.embed`` [vocab, layers * dim] with a token input, ``loop.in`` [width, 2 width] when the config loops, and per
+    layer ``l<i>.{norm1, norm1b, norm2, norm2b}`` (each with ``.b`` and ``.alpha``), ``l<i>.side.{gate, proj, norm}`` and the mixer under
+    ``l<i>.mix.``: attention ``q, k, v`` (each with ``.b``), ``sink``, ``g``, ``o``; latent attention ``dq``, ``dq.norm``, ``uq``, ``dkv``,
+    ``dkv.norm``, ``uk``, ``uv``, ``g``, ``o``; the feed-forward under ``l<i>.mlp.``: ``gate, up, down`` or ``router`` (+ ``.b``),
+    ``e<j>.{gate, up, down}``, ``shared.{gate, up, down, sg}``."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed * 1000003 + 515151)
+    td, H = TORCH_DTYPES[dtype], cfg.hidden_size
+
+    def rn(*shape, s=std):
+        return (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * s).to(td)
+
+    def ru(*shape, lo=0.0, hi=1.0):
+        return (torch.rand(shape, generator=gen, device=device, dtype=torch.float32) * (hi - lo) + lo).to(td)
+
+    def norm(name, sd):
+        sd[name], sd[name + ".b"], sd[name + ".alpha"] = ru(H, lo=0.8, hi=1.2), rn(H, s=0.1), ru(lo=0.5, hi=1.5).reshape(())
+
+    sd = {"embed": rn(cfg.vocab_size, H, s=1.0), "head": rn(cfg.vocab_size, H, s=4.0 * std)}
+    norm("final.norm", sd)
+    if cfg.token_side_dim:
+        sd["side.embed"] = rn(cfg.vocab_size, cfg.token_side_dim * len(cfg.layers), s=1.0)
+    if cfg.loop:
+        sd["loop.in"] = (torch.cat([torch.eye(H), torch.zeros(H, H)], 1).to(device) * 0.8 + torch.randn((H, 2 * H), generator=gen, device=device) * (0.5 / H ** 0.5)).to(td)
+    for i, sp in enumerate(cfg.layers):
+        p, m = cfg.layer_name(i), cfg.layer_name(i) + ".mix"
+        norm(f"{p}.norm1", sd)
+        norm(f"{p}.norm1b", sd)
+        sd[f"{m}.o"] = rn(H, sp.inner, s=4 * std)
+        if sp.type == "sink_attention":
+            sq, skv, svv = sp.heads * sp.dim, sp.n_kv * sp.dim, sp.n_kv * sp.vdim
+            sd[f"{m}.q"], sd[f"{m}.k"], sd[f"{m}.v"] = rn(sq, H, s=4 * std), rn(skv, H, s=4 * std), rn(svv, H, s=4 * std)
+            sd[f"{m}.q.b"], sd[f"{m}.k.b"], sd[f"{m}.v.b"] = rn(sq, s=0.2), rn(skv, s=0.2), rn(svv, s=0.2)
+            sd[f"{m}.sink"], sd[f"{m}.g"] = rn(sp.heads, s=1.0), rn(sp.inner, H, s=2 * std)
+        else:
+            sd[f"{m}.dq"], sd[f"{m}.dq.norm"], sd[f"{m}.uq"] = rn(sp.q_rank, H, s=4 * std), ru(sp.q_rank, lo=0.8, hi=1.2), rn(sp.heads * sp.dim, sp.q_rank, s=0.3)
+            sd[f"{m}.dkv"], sd[f"{m}.dkv.norm"] = rn(sp.kv_rank, H, s=4 * std), ru(sp.kv_rank, lo=0.8, hi=1.2)
+            sd[f"{m}.uk"], sd[f"{m}.uv"] = rn(sp.heads * sp.dim, sp.kv_rank, s=0.3), rn(sp.inner, sp.kv_rank, s=0.3)
+            sd[f"{m}.g"] = rn(sp.heads, H, s=2 * std)
+        mo = sp.moe
+        if sp.dense_ff or mo is not None:
+            norm(f"{p}.norm2", sd)
+            norm(f"{p}.norm2b", sd)
+        if sp.dense_ff:
+            sd[f"{p}.mlp.gate"], sd[f"{p}.mlp.up"], sd[f"{p}.mlp.down"] = rn(sp.dense_ff, H, s=4 * std), rn(sp.dense_ff, H, s=4 * std), rn(H, sp.dense_ff, s=4 * std)
+        elif mo is not None:
+            sd[f"{p}.mlp.router"], sd[f"{p}.mlp.router.b"] = rn(mo.experts, H, s=router_std), rn(mo.experts, s=0.5)
+            for j in range(mo.experts):
+                sd[f"{p}.mlp.e{j}.gate"], sd[f"{p}.mlp.e{j}.up"], sd[f"{p}.mlp.e{j}.down"] = rn(mo.ff, H, s=8 * std), rn(mo.ff, H, s=8 * std), rn(H, mo.ff, s=4 * std)
+            if mo.shared_ff:
+                sd[f"{p}.mlp.shared.gate"], sd[f"{p}.mlp.shared.up"] = rn(mo.shared_ff, H, s=8 * std), rn(mo.shared_ff, H, s=8 * std)
+                sd[f"{p}.mlp.shared.down"], sd[f"{p}.mlp.shared.sg"] = rn(H, mo.shared_ff, s=4 * std), rn(1, H, s=4 * std)
+        if sp.side_dim:
+            sd[f"{p}.side.gate"], sd[f"{p}.side.proj"], sd[f"{p}.side.norm"] = rn(sp.side_dim, H, s=4 * std), rn(H, sp.side_dim, s=0.3), ru(H, lo=0.2, hi=0.6)
+    return sd

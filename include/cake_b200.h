@@ -213,7 +213,28 @@ int cake_b200_block_load_spec(cake_b200_ctx *, int layer_idx, const cake_b200_la
  *                            S <- exp(f + m - m') S + exp(i - m') k v^T, n likewise with k alone; o = S^T q / (max(|n . q|,
  *                            exp(-m')) + 1e-6); o of every head divided by its root mean square, times norm [heads * vdim], times
  *                            sigmoid(g h), then o.  S, n and m live in the cache in fp32.
+ *   CAKE_B200_MIX_SINK_ATTENTION  grouped-query softmax attention with a sliding window that keeps the sequence's first tokens and a
+ *                            learned sink.  q / k / v with biases (q_b, k_b, v_b); the first rot.dims entries of every q and k head are
+ *                            rotated (pairs i, i + dims / 2; optional frequency blend), then, with qk_unit, every head of q and k is
+ *                            divided by its root mean square (eps of the ctx); score = (q . k) * scale; row i sees key j <= i when
+ *                            window == 0, i - j < window or j < keep_first; the softmax's denominator also holds exp(sink_h) (sink
+ *                            [heads], no key, no value; NULL = none); the concatenated heads are multiplied by sigmoid(g h)
+ *                            (g [heads * vdim, hidden]; NULL = none); then o.  K and V rows live in the cache.
+ *   CAKE_B200_MIX_LATENT_WINDOW  latent attention without positions: c_q = rms(dq h) * dq_norm ([q_rank]), q = uq c_q ([heads * dim,
+ *                            q_rank]); c = rms(dkv h) * dkv_norm ([kv_rank]) is the only cached row; per head k = uk c, v = uv c
+ *                            (computed in the absorbed form: the query goes through uk, the weighted latent through uv);
+ *                            score = (q . k) * scale over the window (as above, keep_first included); head h's output is
+ *                            multiplied by sigmoid(g h)_h (g [heads, hidden]; NULL = none); then o.
  * Block structure switches (all 0 / NULL for the plain pre-norm block above):
+ *   norm_kind    0: RMS norms; 1: the element-wise squashing norm tanh(alpha x) * w + b for norm1 / post1 / norm2 / post2, alpha =
+ *                norm_alpha[0..3] in that order, offsets norm1_b / post1_b / norm2_b / post2_b ([hidden])
+ *   side_dim     > 0: after the feed-forward the stream receives a per-layer token input: e = columns [side_col, side_col +
+ *                side_dim) of the token's row of the ctx's side table (cake_b200_embed_tables.side), g = gelu_tanh(side_gate x) * e
+ *                (side_gate [side_dim, hidden]), y = side_proj g ([hidden, side_dim]), x += y / rms(y) * side_norm ([hidden]).
+ *                The ids are those of the step's cake_b200_embed call
+ *   With these two, or with the two mixers above, the routed feed-forward (moe) may follow post-norm blocks as well; moe.logit_bias
+ *   1: `correction` is added to the router's logits, the `top` largest logits are chosen and weighted by the softmax over the
+ *   chosen alone; moe.act 2 is the clamped form with moe.limit (routed experts) / moe.shared_limit (shared expert)
  *   norm_offset  the gains of norm1 / norm2 / post1 / post2 are stored as offsets: gain = stored + norm_offset (computed in fp32)
  *   post1, post2 an RMS norm of the mixer's / feed-forward's output before it is added to the stream
  *   canon_taps   >= 1: the mixer reads h + conv(h), a causal convolution over time per channel of the normed input (canon
@@ -229,6 +250,8 @@ int cake_b200_block_load_spec(cake_b200_ctx *, int layer_idx, const cake_b200_la
 #define CAKE_B200_MIX_DELTA 4
 #define CAKE_B200_MIX_TALKING_ATTENTION 5
 #define CAKE_B200_MIX_MATRIX_MEMORY 6
+#define CAKE_B200_MIX_SINK_ATTENTION 7
+#define CAKE_B200_MIX_LATENT_WINDOW 8
 typedef struct cake_b200_rotary_spec {
   int dims;            /* 0 = no rotation */
   double base;
@@ -240,7 +263,9 @@ typedef struct cake_b200_moe_spec {
   int experts, identity, top;
   float scale;
   int ff, shared_ff;
-  int act;             /* 0 silu, 1 tanh-gelu */
+  int act;             /* 0 silu, 1 tanh-gelu, 2 clamped (limit / shared_limit) */
+  float limit, shared_limit;
+  int logit_bias;
 } cake_b200_moe_spec;
 typedef struct cake_b200_mixer_spec {
   int kind;
@@ -260,6 +285,12 @@ typedef struct cake_b200_mixer_spec {
   int dense_ff, dense_act;
   float dense_limit;
   const struct cake_b200_mixer_spec *side;
+  int window, keep_first; /* sink attention, windowed latent attention: 0 = every earlier key */
+  int qk_unit;            /* sink attention: unit-RMS q and k heads */
+  int q_rank;             /* windowed latent attention */
+  int norm_kind;
+  float norm_alpha[4];
+  int side_dim, side_col;
 } cake_b200_mixer_spec;
 typedef struct cake_b200_mixer_tensors {
   const void *norm1, *norm2;                 /* [hidden]; norm2 NULL without a feed-forward */
@@ -276,12 +307,19 @@ typedef struct cake_b200_mixer_tensors {
   const void *ff_gate, *ff_up, *ff_down;     /* dense feed-forward */
   const void *branch_norm;                   /* [hidden]: with a side mixer, the gain of this mixer's output norm */
   const struct cake_b200_mixer_tensors *side;
+  const void *sink;                          /* sink attention: [heads] */
+  const void *dq, *dq_norm, *uq;             /* windowed latent attention: [q_rank, hidden], [q_rank], [heads * dim, q_rank] */
+  const void *norm1_b, *post1_b, *norm2_b, *post2_b;  /* norm_kind 1: [hidden] each */
+  const void *side_gate, *side_proj, *side_norm;      /* side_dim > 0: [side_dim, hidden], [hidden, side_dim], [hidden] */
 } cake_b200_mixer_tensors;
 int cake_b200_block_load_mixer(cake_b200_ctx *, int layer_idx, const cake_b200_mixer_spec *, const cake_b200_mixer_tensors *,
                                cake_b200_block **out);
 /* Between blocks of a looped range: x <- x + (x0 ? x0 : 0) + vec, rows of [hidden] fp32; vec [hidden] in D, host or device
  * memory on the first call with that pointer (it is uploaded once and kept by the ctx under `slot`, 0 <= slot < 64). */
 int cake_b200_stream_inject(cake_b200_ctx *, float *x_dev, const float *x0_dev, const void *vec, int slot, int rows);
+/* In front of a pass of a looped range: x <- W [x; x0], rows of [hidden] fp32, W [hidden, 2 * hidden] in D (x's half first), host
+ * or device memory on the first call with that pointer (uploaded once and kept by the ctx). */
+int cake_b200_stream_project(cake_b200_ctx *, float *x_dev, const float *x0_dev, const void *w, int rows);
 
 /* ---- cache ------------------------------------------------------------------------------------ */
 int cake_b200_cache_create(cake_b200_ctx *, int batch, int max_seq, cake_b200_cache **out);
@@ -322,6 +360,11 @@ typedef struct cake_b200_embed_tables {
   const void *pos;
   int pos_rows;
   float final_norm_offset;
+  const void *side;         /* [vocab, side_cols]: the per-layer token inputs of every layer side by side, or NULL */
+  int side_cols;
+  int final_norm_kind;      /* 1: the final norm is tanh(final_alpha x) * ln_f + final_bias ([hidden]) */
+  float final_alpha;
+  const void *final_bias;
 } cake_b200_embed_tables;
 int cake_b200_head_load_tables(cake_b200_ctx *, const cake_b200_embed_tables *);
 int cake_b200_embed_at(cake_b200_ctx *, cake_b200_cache *, const uint32_t *ids_host, int batch, int seq, int index_pos, void *x_dev);
