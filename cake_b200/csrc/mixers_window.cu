@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -300,8 +301,201 @@ int window_attention(cudaStream_t st, int dtype, const WindowAttn &p, uint64_t *
   MX_DONE(split ? 2 : 1);
 }
 
-bool window_attention_tiled_ok(int, const WindowAttn &) { return false; }
-int window_attention_tiled(cudaStream_t, int, const WindowAttn &, uint64_t *) { return (int)cudaErrorInvalidValue; }
+// ---------------------------------------------------------------------------------------------- window attention, tiled
+// A CTA of four warps owns 64 consecutive rows of one (batch row, head); every warp 16 of them.  Keys come in tiles of 64: first
+// the kept first tokens that lie before the window of the block's first row, then the window up to the block's last row; the
+// visibility rule is applied per score, so a tile may straddle any edge.  Scores are 16 x 8 x 16 tensor-core products of the
+// staged q and key tiles with fp32 accumulators; the running softmax is fp32 per row (a quad of lanes shares a row); the weights
+// enter the second product as w_hi + w_lo in D (about 16 mantissa bits), the values through transposing shared-memory loads.
+// Head sizes are padded to the template's with zero columns in shared memory.
+constexpr int WT_ROWS = 64, WT_KEYS = 64;
+template <typename T> __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma16816<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// rows [r0, r0 + 64) of a [*, width] matrix with row stride ld into a tile with row stride LDS; rows >= n_rows and columns >= width
+// are zeros (width is a multiple of 8: 16-byte pieces)
+template <typename T, int LDS, int COLS>
+__device__ __forceinline__ void stage_tile(T *dst, const T *src, long ld, int n_rows, int width) {
+  constexpr int PIECES = COLS / 8;
+  for (int i = threadIdx.x; i < 64 * PIECES; i += blockDim.x) {
+    const int r = i / PIECES, c = (i % PIECES) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < n_rows && c < width) v = *reinterpret_cast<const uint4 *>(src + (long)r * ld + c);
+    *reinterpret_cast<uint4 *>(dst + r * LDS + c) = v;
+  }
+}
+template <typename T, int HD>
+__global__ void __launch_bounds__(128) window_attn_tiled_kernel(const WindowAttn p) {
+  constexpr int LDS = HD + 8, KS = HD / 16, NV = HD / 8;
+  extern __shared__ __align__(16) unsigned char wt_smem[];
+  T *qs = reinterpret_cast<T *>(wt_smem), *ks = qs + 64 * LDS, *vs = ks + 64 * LDS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, qd = lane & 3;
+  const int r0 = blockIdx.x * WT_ROWS, h = blockIdx.y, b = blockIdx.z, g = h / (p.heads / p.kv_heads);
+  const int n_rows = min(WT_ROWS, p.S - r0), p0 = p.pos0 + r0, p1 = p0 + n_rows - 1;
+  const T *q = reinterpret_cast<const T *>(p.q) + ((size_t)b * p.S + r0) * p.ldq + (size_t)h * p.dim;
+  const T *kc = reinterpret_cast<const T *>(p.kc) + ((size_t)b * p.kv_heads + g) * p.cap * p.dim;
+  const T *vc = reinterpret_cast<const T *>(p.vc) + ((size_t)b * p.kv_heads + g) * p.cap * p.vdim;
+  stage_tile<T, LDS, HD>(qs, q, p.ldq, n_rows, p.dim);
+  __syncthreads();
+  uint32_t qf[KS][4];
+#pragma unroll
+  for (int kk = 0; kk < KS; kk++) {
+    const T *base = qs + (warp * 16 + gid) * LDS + kk * 16 + 2 * qd;
+    qf[kk][0] = *reinterpret_cast<const uint32_t *>(base);
+    qf[kk][1] = *reinterpret_cast<const uint32_t *>(base + 8 * LDS);
+    qf[kk][2] = *reinterpret_cast<const uint32_t *>(base + 8);
+    qf[kk][3] = *reinterpret_cast<const uint32_t *>(base + 8 * LDS + 8);
+  }
+  float o[NV][4];
+#pragma unroll
+  for (int n = 0; n < NV; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+  const int row_pos[2] = {p0 + warp * 16 + gid, p0 + warp * 16 + gid + 8};
+  const int lo = p.window > 0 ? max(0, p0 - p.window + 1) : 0;
+  const int nA = min(p.keep_first, lo);
+  const int tilesA = (nA + WT_KEYS - 1) / WT_KEYS, tilesB = (p1 - lo + 1 + WT_KEYS - 1) / WT_KEYS;
+  for (int tl = 0; tl < tilesA + tilesB; tl++) {
+    const int j0 = tl < tilesA ? tl * WT_KEYS : lo + (tl - tilesA) * WT_KEYS;
+    const int jend = tl < tilesA ? nA : p1 + 1;            // keys of this tile: [j0, min(j0 + 64, jend))
+    const int nk = min(WT_KEYS, jend - j0);
+    __syncthreads();                                        // the previous tile has been consumed
+    stage_tile<T, LDS, HD>(ks, kc + (size_t)j0 * p.dim, p.dim, nk, p.dim);
+    stage_tile<T, LDS, HD>(vs, vc + (size_t)j0 * p.vdim, p.vdim, nk, p.vdim);
+    __syncthreads();
+    float sc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; n++) {
+      sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < KS; kk++) {
+        const T *kb = ks + (n * 8 + gid) * LDS + kk * 16 + 2 * qd;
+        mma16816<T>(sc[n], qf[kk], *reinterpret_cast<const uint32_t *>(kb), *reinterpret_cast<const uint32_t *>(kb + 8));
+      }
+    }
+    // visibility, scale, running maximum
+    float mnew[2] = {mrow[0], mrow[1]};
+#pragma unroll
+    for (int n = 0; n < 8; n++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int j = j0 + n * 8 + 2 * qd + (e & 1), i = row_pos[e >> 1];
+        const bool vis = j < jend && j <= i && (p.window == 0 || i - j < p.window || j < p.keep_first);
+        sc[n][e] = vis ? sc[n][e] * p.scale : -INFINITY;
+        mnew[e >> 1] = fmaxf(mnew[e >> 1], sc[n][e]);
+      }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      mnew[r] = fmaxf(mnew[r], __shfl_xor_sync(0xffffffffu, mnew[r], 1));
+      mnew[r] = fmaxf(mnew[r], __shfl_xor_sync(0xffffffffu, mnew[r], 2));
+      corr[r] = mnew[r] == -INFINITY ? 1.f : expf(mrow[r] - mnew[r]);
+      mrow[r] = mnew[r];
+      lrow[r] *= corr[r];
+    }
+#pragma unroll
+    for (int n = 0; n < NV; n++) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+    // weights as w_hi + w_lo in D, in the first operand's layout: score tiles 2 kk and 2 kk + 1 form the k-step kk
+    uint32_t wh[4][4], wl[4][4];
+#pragma unroll
+    for (int n = 0; n < 8; n++) {
+      float w[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        w[e] = mrow[e >> 1] == -INFINITY ? 0.f : expf(sc[n][e] - mrow[e >> 1]);
+        lrow[e >> 1] += w[e];
+      }
+      const int kk = n >> 1, off = (n & 1) * 2;
+      wh[kk][off] = pack2x<T>(w[0], w[1]);
+      wh[kk][off + 1] = pack2x<T>(w[2], w[3]);
+      wl[kk][off] = pack2x<T>(w[0] - rnd<T>(w[0]), w[1] - rnd<T>(w[1]));
+      wl[kk][off + 1] = pack2x<T>(w[2] - rnd<T>(w[2]), w[3] - rnd<T>(w[3]));
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; kk++)
+#pragma unroll
+      for (int n = 0; n < NV; n++) {
+        uint32_t b0, b1;
+        const T *vrow = vs + (kk * 16 + (lane & 15)) * LDS + n * 8;
+        const uint32_t addr = (uint32_t)__cvta_generic_to_shared(vrow);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(addr));
+        mma16816<T>(o[n], wh[kk], b0, b1);
+        mma16816<T>(o[n], wl[kk], b0, b1);
+      }
+  }
+  // the sink joins the denominator; normalise, gate, store
+  const T *gate = reinterpret_cast<const T *>(p.gate);
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+    float l = lrow[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    float m = mrow[r], f = 1.f;
+    if (p.sink) {
+      const float sk = DT<T>::to_f(reinterpret_cast<const T *>(p.sink)[h]);
+      const float mt = fmaxf(m, sk);
+      f = m == -INFINITY ? 0.f : expf(m - mt);
+      l = l * f + expf(sk - mt);
+    }
+    const int row = warp * 16 + gid + 8 * r;
+    if (row >= n_rows) continue;
+    const float il = f / l;
+    const size_t mrow_idx = (size_t)b * p.S + r0 + row;
+    const float gh = gate && p.gate_per_head ? sigmoid_f(DT<T>::to_f(gate[mrow_idx * p.ldg + h])) : 1.f;
+    T *out = reinterpret_cast<T *>(p.out) + mrow_idx * p.ldo + (size_t)h * p.vdim;
+#pragma unroll
+    for (int n = 0; n < NV; n++) {
+      const int c = n * 8 + 2 * qd;
+      if (c >= p.vdim) continue;
+      float v0 = o[n][2 * r] * il, v1 = o[n][2 * r + 1] * il;
+      if (gate) {
+        v0 *= p.gate_per_head ? gh : sigmoid_f(DT<T>::to_f(gate[mrow_idx * p.ldg + (size_t)h * p.vdim + c]));
+        v1 *= p.gate_per_head ? gh : sigmoid_f(DT<T>::to_f(gate[mrow_idx * p.ldg + (size_t)h * p.vdim + c + 1]));
+      }
+      *reinterpret_cast<uint32_t *>(out + c) = pack2x<T>(v0, v1);
+    }
+  }
+}
+template <> __global__ void window_attn_tiled_kernel<float, 32>(const WindowAttn) {}
+template <> __global__ void window_attn_tiled_kernel<float, 64>(const WindowAttn) {}
+template <> __global__ void window_attn_tiled_kernel<float, 128>(const WindowAttn) {}
+
+bool window_attention_tiled_ok(int dtype, const WindowAttn &p) {
+  static const bool off = []() {
+    const char *e = getenv("CAKE_B200_NO_TC"), *f = getenv("CAKE_B200_NO_TILED_ATTN");
+    return (e && e[0] == '1') || (f && f[0] == '1');
+  }();
+  const int D = p.dim > p.vdim ? p.dim : p.vdim;
+  return !off && dtype != 2 && p.S >= 16 && D <= 128 && p.dim % 8 == 0 && p.vdim % 8 == 0 && p.ldq % 8 == 0 && p.ldo % 2 == 0 && p.heads % p.kv_heads == 0 &&
+         ((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.kc & 15) == 0 && ((uintptr_t)p.vc & 15) == 0 && ((uintptr_t)p.out & 3) == 0;
+}
+template <typename T, int HD> static cudaError_t launch_window_tiled(cudaStream_t st, const WindowAttn &p) {
+  const size_t smem = (size_t)3 * 64 * (HD + 8) * sizeof(T);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(window_attn_tiled_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  window_attn_tiled_kernel<T, HD><<<dim3((p.S + WT_ROWS - 1) / WT_ROWS, p.heads, p.B), 128, smem, st>>>(p);
+  return cudaSuccess;
+}
+int window_attention_tiled(cudaStream_t st, int dtype, const WindowAttn &p, uint64_t *launches) {
+  if (!window_attention_tiled_ok(dtype, p)) return (int)cudaErrorInvalidValue;
+  const int D = p.dim > p.vdim ? p.dim : p.vdim;
+  cudaError_t e = cudaSuccess;
+  if (dtype == 1) e = D <= 32 ? launch_window_tiled<__half, 32>(st, p) : D <= 64 ? launch_window_tiled<__half, 64>(st, p) : launch_window_tiled<__half, 128>(st, p);
+  else e = D <= 32 ? launch_window_tiled<__nv_bfloat16, 32>(st, p) : D <= 64 ? launch_window_tiled<__nv_bfloat16, 64>(st, p) : launch_window_tiled<__nv_bfloat16, 128>(st, p);
+  if (e != cudaSuccess) return (int)e;
+  MX_DONE(1);
+}
 
 // ---------------------------------------------------------------------------------------------- per-layer token input
 template <typename T>

@@ -320,9 +320,9 @@ def make_netolorn_checkpoint(cfg: Config, dtype: str = "bf16", seed: int = 1234,
             sd[f"{m}.q.b"], sd[f"{m}.k.b"], sd[f"{m}.v.b"] = rn(sq, s=0.2), rn(skv, s=0.2), rn(svv, s=0.2)
             sd[f"{m}.sink"], sd[f"{m}.g"] = rn(sp.heads, s=1.0), rn(sp.inner, H, s=2 * std)
         else:
-            sd[f"{m}.dq"], sd[f"{m}.dq.norm"], sd[f"{m}.uq"] = rn(sp.q_rank, H, s=4 * std), ru(sp.q_rank, lo=0.8, hi=1.2), rn(sp.heads * sp.dim, sp.q_rank, s=0.3)
+            sd[f"{m}.dq"], sd[f"{m}.dq.norm"], sd[f"{m}.uq"] = rn(sp.q_rank, H, s=4 * std), ru(sp.q_rank, lo=0.8, hi=1.2), rn(sp.heads * sp.dim, sp.q_rank, s=sp.q_rank ** -0.5)
             sd[f"{m}.dkv"], sd[f"{m}.dkv.norm"] = rn(sp.kv_rank, H, s=4 * std), ru(sp.kv_rank, lo=0.8, hi=1.2)
-            sd[f"{m}.uk"], sd[f"{m}.uv"] = rn(sp.heads * sp.dim, sp.kv_rank, s=0.3), rn(sp.inner, sp.kv_rank, s=0.3)
+            sd[f"{m}.uk"], sd[f"{m}.uv"] = rn(sp.heads * sp.dim, sp.kv_rank, s=sp.kv_rank ** -0.5), rn(sp.inner, sp.kv_rank, s=sp.kv_rank ** -0.5)
             sd[f"{m}.g"] = rn(sp.heads, H, s=2 * std)
         mo = sp.moe
         if sp.dense_ff or mo is not None:
