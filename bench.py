@@ -10,6 +10,7 @@ Llama-3-8B bf16, bs=1, 2k context, layers sharded over N GPUs of one box (N=1 ->
     python bench.py --workload nigenex [--sizes 2k,4k,4k-hd64]    # the Nigenex design beside the closest existing block
     python bench.py --workload setodra [--sizes 1k,2k]            # the Setodra design beside the closest existing model
     python bench.py --workload nuvarax [--sizes 1k,2k]            # the Nuvarax design beside the closest existing model
+    python bench.py --workload netolorn [--sizes 1k,2k]           # the Netolorn design beside the closest existing models
 
 A "step" is one decoded token: one pass of the hot path (embed -> blocks -> ln_f/lm_head/argmax) at batch 1.
 tok/s follows the reference's definition (master.rs:131-166): prefill excluded.  Prints ONE JSON line (rank 0).
@@ -1277,6 +1278,114 @@ def nuvarax_leg(env: Env, sizes=("1k", "2k"), batch: int = 4, seq: int = 4096, c
             "peaks": {"tensor_tflops": pk["tc"], "hbm_gbs": pk["hbm"], "source": pk["src"]}, "sizes": out}
 
 
+NETOLORN_SIZES = {  # layer sizes of real models (random weights): sink attention + dense feed-forward, windowed latent attention + routed feed-forward
+    "1k": dict(width=1024, ff=4224, window=1024, keep_first=4, side=128,
+               att=dict(heads=8, kv_heads=2, dim=128, vdim=128, rot_dims=64),
+               lat=dict(heads=8, dim=128, vdim=128, q_rank=384, kv_rank=512), moe=dict(experts=32, top=4, ff=704, shared_ff=1408)),
+    "2k": dict(width=2048, ff=11264, window=1024, keep_first=4, side=128,
+               att=dict(heads=16, kv_heads=4, dim=128, vdim=128, rot_dims=64),
+               lat=dict(heads=16, dim=128, vdim=128, q_rank=768, kv_rank=512), moe=dict(experts=64, top=6, ff=1408, shared_ff=2816)),
+}
+
+
+def netolorn_leg(env: Env, sizes=("1k", "2k"), batch: int = 4, seq: int = 4096, ctx_len: int = 2048, steps: int = 32, reps: int = 3) -> dict:
+    """`--workload netolorn`: the Netolorn design (mixer-list blocks with squashing norms on both sides of every sublayer and a
+    per-layer token input) in three 4-layer models per size, each beside the framework's closest existing model at equal width:
+      attention   4 x (grouped-query attention with a partial rotation, unit-RMS q / k, a window that keeps the first tokens, a sink
+                  and an output gate + dense feed-forward)  beside Nigenex (windowed grouped-query attention + dense feed-forward)
+      latent      4 x (windowed latent attention without positions + routed clamped feed-forward with a shared expert)  beside the
+                  Setodra-style latent attention layer (+ routed feed-forward of the same sizes)
+      mixed       attention, latent, attention, latent (the headline number; no counterpart)
+    all through TextModelBase / forward_batch.  Workload and timing as in the Setodra leg."""
+    import torch
+    from cake_b200.config import Config, LayerSpec, MixerSpec, MoeSpec, RotarySpec
+    from cake_b200.synth import make_listed_checkpoint, make_mixer_checkpoint, make_netolorn_checkpoint
+    pk = peaks()
+    out, launches, vocab = {}, 0, 32768
+    mseq = max(seq, ctx_len + steps + 8)
+    for name in sizes:
+        z = NETOLORN_SIZES[name]
+        W, ff, win, keep, side, a, la, mo = z["width"], z["ff"], z["window"], z["keep_first"], z["side"], z["att"], z["lat"], z["moe"]
+        ff_act = mo["top"] * mo["ff"] + mo["shared_ff"]
+        keys_win = lambda S: sum(min(i + 1, win) for i in range(S))
+        keys_kept = lambda S: sum(min(keep, max(0, i + 1 - win)) for i in range(S))
+        att_layer = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+                     "mixer": {"heads": a["heads"], "kv_heads": a["kv_heads"], "dim": a["dim"], "vdim": a["vdim"], "scale": a["dim"] ** -0.5,
+                               "mask": {"size": win, "keep_first": keep},
+                               "rot": {"dims": a["rot_dims"], "base": 10000.0, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+        lat_layer = {"type": "latent_attention",
+                     "mlp": {"kind": "moe", "router": {"experts": mo["experts"], "top": mo["top"]}, "expert": {"ff": mo["ff"], "limit": 7.0},
+                             "shared": {"ff": mo["shared_ff"], "limit": 7.0}},
+                     "mixer": {"heads": la["heads"], "dim": la["dim"], "vdim": la["vdim"], "q_rank": la["q_rank"], "kv_rank": la["kv_rank"],
+                               "scale": la["dim"] ** -0.5, "mask": {"size": win}}}
+        # algorithmic work per token and layer: products [flops], weights read by one decoded token [bytes], cache rows read [bytes]
+        Ha, Ga, Hl, R = a["heads"], a["kv_heads"], la["heads"], la["kv_rank"]
+        side_f = 2.0 * W * 2 * side
+        att_lin = 2.0 * W * (Ha * a["dim"] + Ga * (a["dim"] + a["vdim"]) + 2 * Ha * a["vdim"]) + 2.0 * W * 3 * ff + side_f
+        lat_lin = (2.0 * W * (la["q_rank"] + R + Hl + Hl * la["vdim"]) + 2.0 * la["q_rank"] * Hl * la["dim"] + 2.0 * Hl * R * (la["dim"] + la["vdim"])
+                   + 2.0 * W * 3 * ff_act + 2.0 * W * (mo["experts"] + 1) + side_f)
+        att_key, lat_key = 2.0 * Ha * (a["dim"] + a["vdim"]), 2.0 * Hl * 2 * R
+        att_cache = 2.0 * Ga * (a["dim"] + a["vdim"]) * (min(win, ctx_len) + keep)
+        lat_cache = 2.0 * R * min(win, ctx_len)
+        row = {"size": z}
+        for arch in ("attention", "attention_closest", "latent", "latent_closest", "mixed"):
+            if arch in ("attention", "latent", "mixed"):
+                order = {"attention": [att_layer] * 4, "latent": [lat_layer] * 4, "mixed": [att_layer, lat_layer, att_layer, lat_layer]}[arch]
+                cfg = Config.from_hf({"architecture": "Netolorn", "width": W, "vocab": vocab, "norm": {"eps": 1e-6}, "token_side": {"dim": side}, "layers": order})
+                cfg.max_seq_len = mseq
+                sd = make_netolorn_checkpoint(cfg, "bf16", seed=5, device=env.dev, std=0.02)
+                n_att = sum(1 for L in order if L["type"] == "attention")
+                flop_tok = n_att * att_lin + (4 - n_att) * lat_lin
+                att_flops = lambda S, n_att=n_att: (n_att * att_key + (4 - n_att) * lat_key) * keys_win(S) + n_att * att_key * keys_kept(S)
+                dbytes = flop_tok + n_att * att_cache + (4 - n_att) * lat_cache   # a weight is read once per decoded token: 2 bytes = 2 flops
+            elif arch == "attention_closest":
+                spec = LayerSpec(heads=Ha, kv_heads=Ga, head_dim=a["dim"], window=win, scale=a["dim"] ** -0.5, softcap=30.0, ff=ff)
+                cfg = Config(hidden_size=W, intermediate_size=ff, vocab_size=vocab, num_hidden_layers=4, num_attention_heads=Ha, num_key_value_heads=Ga,
+                             head_dim=a["dim"], max_seq_len=mseq, block_kind="nigenex", layers=[spec] * 4, logit_softcap=30.0, model_prefix="")
+                sd = make_listed_checkpoint(cfg, "bf16", seed=5, device=env.dev, std=0.02)
+                flop_tok = 4 * 2.0 * W * ((Ha + Ga) * a["dim"] + Ha + 3 * ff + Ha * a["dim"])
+                att_flops = lambda S: 4 * 4.0 * Ha * a["dim"] * keys_win(S)
+                dbytes = flop_tok + 4 * 2.0 * Ga * a["dim"] * min(win, ctx_len)
+            else:
+                rd = 64
+                m = MoeSpec(scale=2.5, experts=mo["experts"], identity=0, top=mo["top"], ff=mo["ff"], shared_ff=mo["shared_ff"])
+                rot = RotarySpec(dims=rd, base=10000.0, factor=8.0, fast=32.0, slow=1.0, original=2048)
+                lat = lambda: MixerSpec(type="latent_attention", scale=(la["dim"] + rd) ** -0.5, rot=rot, moe=m, heads=Hl, dim=la["dim"], rot_dim=rd,
+                                        vdim=la["vdim"], kv_rank=R)
+                layers = [lat(), lat(), lat(), lat()]
+                cfg = Config(hidden_size=W, intermediate_size=0, vocab_size=vocab, num_hidden_layers=4, num_attention_heads=Hl, num_key_value_heads=Hl,
+                             rms_norm_eps=1e-6, head_dim=128, max_seq_len=mseq, block_kind="setodra", layers=layers, model_prefix="", embed_scale=1.0)
+                sd = make_mixer_checkpoint(cfg, "bf16", seed=5, device=env.dev, std=0.02)
+                n_lat = Hl * (la["dim"] + rd) + R + rd
+                flop_tok = 4 * (2.0 * W * (n_lat + Hl * la["vdim"]) + 2.0 * Hl * R * (la["dim"] + la["vdim"]) + 2.0 * W * 3 * ff_act + 2.0 * W * mo["experts"])
+                att_flops = lambda S: 4 * 2.0 * Hl * (2 * R + rd) * (S * (S + 1) // 2)   # no window: every earlier latent row
+                dbytes = flop_tok + 4 * 2.0 * ctx_len * (R + rd)
+            t = _time_listed_model(env, cfg, sd, batch, seq, ctx_len, steps, reps, mseq)
+            del sd
+            torch.cuda.empty_cache()
+            launches += t["launches"]
+            M, ms, dms = batch * seq, t["prefill"]["ms"], t["decode"]["ms_per_token"]
+            flops = flop_tok * M + batch * att_flops(seq) + 2.0 * batch * vocab * W
+            dbytes += 2.0 * vocab * W
+            row[arch] = {"prefill": {"tok_s": M / (ms / 1e3), "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+                                     "frac_of_tensor_peak": flops / (ms * 1e-3) / 1e12 / pk["tc"], "finite": t["prefill"]["finite"],
+                                     "launches": t["prefill"]["launches"]},
+                         "decode": {"tok_s": 1e3 / dms, "ms_per_token": dms, "gb_s": dbytes / (dms * 1e-3) / 1e9,
+                                    "frac_of_hbm_peak": dbytes / (dms * 1e-3) / 1e9 / pk["hbm"], "launches_per_token": t["decode"]["launches_per_token"],
+                                    "finite": t["decode"]["finite"]}}
+        for kind in ("attention", "latent"):   # how far from the roofline each is, the new design over the closest model (1 = equally far)
+            row[kind + "_prefill_distance"] = row[kind + "_closest"]["prefill"]["frac_of_tensor_peak"] / row[kind]["prefill"]["frac_of_tensor_peak"]
+            row[kind + "_decode_distance"] = row[kind + "_closest"]["decode"]["frac_of_hbm_peak"] / row[kind]["decode"]["frac_of_hbm_peak"]
+        out[name] = row
+    head = out[sizes[-1]]
+    return {"metric": f"netolorn prefill tok/s (4 layers, width {head['size']['width']}, bf16, bs={batch} x {seq})", "value": head["mixed"]["prefill"]["tok_s"],
+            "unit": "tok/s", "ms_per_step": head["mixed"]["prefill"]["ms"], "steps": reps, "warmup": 1, "gpu_launches": int(launches),
+            "config": {"workload": f"Netolorn (attention / latent / mixed layer orders) vs Nigenex and the Setodra latent layer at equal width, 4 layers, bf16, "
+                                   f"prefill bs={batch} x {seq}, decode bs=1 at {ctx_len} context x {steps} steps",
+                       "l2": "prefill activations / decode weights exceed L2"},
+            "peaks": {"tensor_tflops": pk["tc"], "hbm_gbs": pk["hbm"], "source": pk["src"]}, "sizes": out}
+
+
 # ------------------------------------------------------------------------------------------------
 def run_cuda(args):
     env = Env(args)
@@ -1308,6 +1417,16 @@ def run_cuda(args):
                 env.sampler.start()
             sizes = tuple((args.sizes if args.sizes != "2k,4k,4k-hd64" else "1k,2k").split(","))
             line = nuvarax_leg(env, sizes=sizes, batch=args.pf_batch, seq=args.pf_seq, steps=max(4, min(args.steps, 64)))
+            line["clocks"] = env.sampler.stop() if env.sampler else None
+            line.update({"n_gpus": 1, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic"})
+            emit(line)
+        return
+    if args.workload == "netolorn":
+        if rank == 0:
+            if env.sampler:
+                env.sampler.start()
+            sizes = tuple((args.sizes if args.sizes != "2k,4k,4k-hd64" else "1k,2k").split(","))
+            line = netolorn_leg(env, sizes=sizes, batch=args.pf_batch, seq=args.pf_seq, steps=max(4, min(args.steps, 64)))
             line["clocks"] = env.sampler.stop() if env.sampler else None
             line.update({"n_gpus": 1, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic"})
             emit(line)
@@ -1385,9 +1504,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--model", default="8b", choices=["8b", "70b"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "nigenex", "setodra", "nuvarax"])
-    ap.add_argument("--pf-batch", type=int, default=4, help="--workload setodra / nuvarax: batch rows of the prefill step")
-    ap.add_argument("--pf-seq", type=int, default=4096, help="--workload setodra / nuvarax: tokens per row of the prefill step")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "nigenex", "setodra", "nuvarax", "netolorn"])
+    ap.add_argument("--pf-batch", type=int, default=4, help="--workload setodra / nuvarax / netolorn: batch rows of the prefill step")
+    ap.add_argument("--pf-seq", type=int, default=4096, help="--workload setodra / nuvarax / netolorn: tokens per row of the prefill step")
     ap.add_argument("--sizes", default="2k,4k,4k-hd64", help="--workload nigenex: which of NIGENEX_SIZES to run")
     ap.add_argument("--extras", default="auto", choices=["auto", "none", "all"],
                     help="auto: config0 + config4 at N=1, config3 (70B) at N=8; none: the headline only")

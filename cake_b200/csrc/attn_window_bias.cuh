@@ -33,6 +33,12 @@ struct WinAttn {
   void *y;               // [B*S, ldy] D: head h at columns [h*hd, (h+1)*hd)
   int B, S, heads, n_kv, hd, cap, pos0, ld, ldy, gate_col, window;
   float scale, softcap;
+  // attn_window_tc_kernel only (zero = absent):
+  int keep_first;        // keys [0, keep_first) stay visible to every later row, whatever the window
+  int key0;              // the position of row 0 of kc / vc (a buffer that starts at the first key any row of the step sees)
+  const void *sink;      // [heads] D: a logit that joins every row's denominator, without key or value
+  const void *gate;      // gate_mode 1: [B*S, ldg] D logits, one per head at column h; 2: one per output element at h*hd + i
+  int gate_mode, ldg;
 };
 constexpr int WA_MAX_HD = 256;
 

@@ -4,7 +4,9 @@
 //   * the score modifiers applied by the softmax warps before the mask (the modified score is in natural units, so the
 //     exponent constant is log2 e), rows that see nothing in a tile keeping a -inf reference,
 //   * the K tensor map given twice: the keys double as values, the V ring is filled from the same cache rows,
-//   * the head gate and the caller's row stride in the epilogue.
+//   * the head gate and the caller's row stride in the epilogue,
+//   * optionally: the tiles of the kept first keys ahead of the window's tiles, a sink logit in the denominator, a gate per head
+//     or per output element from a buffer of its own, and key / value buffers whose first row is a later position (key0).
 // Warp roles, barriers, TMEM layout and the P_hi + P_lo operand are those of attn_prefill_tc_kernel; see there.
 // Cost model: four MUFU operations per score (tanh = ex2 + rcp, ln, the softmax's ex2) against one in the plain kernel make
 // the softmax warps, not the MMAs, the bound of this kernel.
@@ -37,7 +39,11 @@ attn_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const int kv_end = pos0 + min(S, m0 + FT_BM);  // keys visible to the last query of this tile
   // tiles [j_lo, j_end): from the one that holds the first key the tile's first row sees; rings and phases count from j_lo
   const int j_lo = p.window > 0 ? max(0, pos0 + m0 - p.window + 1) / FT_BN : 0;
-  const int n_tiles = (kv_end + FT_BN - 1) / FT_BN - j_lo;
+  // kept first keys that lie before the window's first tile come first: iteration j works on key tile j (j < n_kept) or
+  // j_lo + j - n_kept
+  const int n_kept = min(j_lo, (p.keep_first + FT_BN - 1) / FT_BN);
+  const int n_tiles = n_kept + (kv_end + FT_BN - 1) / FT_BN - j_lo;
+  const int j_add = j_lo - n_kept;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 13; i++) mbar_init(&bars[i], i == 11 ? 128u : 1u);
@@ -71,12 +77,13 @@ attn_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         unsigned char *kd = k_s + st * FT_KV_BYTES, *vd = v_s + st * FT_KV_BYTES;
         if (j >= 2) mbar_wait(&k_empty[st], eph);
         mbar_arrive_expect_tx(&k_full[st], FT_KV_BYTES);
-        tma_load_3d(kd, &map_k, 0, (j_lo + j) * FT_BN, slab, &k_full[st]);
-        tma_load_3d(kd + FT_KV_BYTES / 2, &map_k, 64, (j_lo + j) * FT_BN, slab, &k_full[st]);
+        const int krow = (j < n_kept ? j : j + j_add) * FT_BN - p.key0;  // rows before the buffer read as zeros and are masked
+        tma_load_3d(kd, &map_k, 0, krow, slab, &k_full[st]);
+        tma_load_3d(kd + FT_KV_BYTES / 2, &map_k, 64, krow, slab, &k_full[st]);
         if (j >= 2) mbar_wait(&v_empty[st], eph);
         mbar_arrive_expect_tx(&v_full[st], FT_KV_BYTES);
-        tma_load_3d(vd, &map_v, 0, (j_lo + j) * FT_BN, slab, &v_full[st]);
-        tma_load_3d(vd + FT_KV_BYTES / 2, &map_v, 64, (j_lo + j) * FT_BN, slab, &v_full[st]);
+        tma_load_3d(vd, &map_v, 0, krow, slab, &v_full[st]);
+        tma_load_3d(vd + FT_KV_BYTES / 2, &map_v, 64, krow, slab, &v_full[st]);
       }
     }
   } else if (warp == 5) {
@@ -149,15 +156,16 @@ attn_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       // the distance is carried as a float (exact below 2^24, no I2F on the MUFU pipe), masked entries take the arithmetic
       // with a clamped distance and are replaced by -inf at the end.
       float mx = -INFINITY;
-      const float fd0 = (float)(qp - (j_lo + j) * FT_BN);  // distance to the tile's first key
+      const float fd0 = (float)(qp - (j < n_kept ? j : j + j_add) * FT_BN);  // distance to the tile's first key
       const float fwin = p.window > 0 ? (float)p.window : 3.0e38f;
+      const float fkept = (float)(qp - p.keep_first);  // key < keep_first  <=>  distance > qp - keep_first
 #pragma unroll
       for (int i = 0; i < FT_BN; i++) {
         const float fd = fd0 - (float)i;
         float v = sv[i] * p.scale;
         if (p.softcap > 0.f) v = p.softcap * (1.0f - __fdividef(2.0f, __expf(v * inv_cap2) + 1.0f));
         if (biased) v -= r1 * __logf(fmaf(r2, fmaxf(fd, 0.f), 1.0f));
-        v = (fd >= 0.f && fd < fwin) ? v : -INFINITY;
+        v = (fd >= 0.f && (fd < fwin || fd > fkept)) ? v : -INFINITY;
         sv[i] = v;
         mx = fmaxf(mx, v);
       }
@@ -216,7 +224,13 @@ attn_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     tc_fence_after();
     const int t = m0 + row;
     float gate = 1.0f;
-    if (p.gate_col >= 0 && t < S) gate = 1.0f / (1.0f + expf(-DT<T>::to_f(reinterpret_cast<const T *>(p.qkg)[(size_t)(b * S + t) * p.ld + p.gate_col + h])));
+    const T *gsrc = reinterpret_cast<const T *>(p.gate) + (size_t)(b * S + t) * p.ldg;
+    if (p.gate_mode == 1) {
+      if (t < S) gate = 1.0f / (1.0f + expf(-DT<T>::to_f(gsrc[h])));
+    } else if (p.gate_mode == 0 && p.gate_col >= 0 && t < S)
+      gate = 1.0f / (1.0f + expf(-DT<T>::to_f(reinterpret_cast<const T *>(p.qkg)[(size_t)(b * S + t) * p.ld + p.gate_col + h])));
+    // the sink counts once in the denominator, relative to the row's reference maximum (which holds at least the row's own key)
+    if (p.sink) l_run += expf(DT<T>::to_f(reinterpret_cast<const T *>(p.sink)[h]) - m_run);
     const float inv = gate / l_run;
     T *dst = reinterpret_cast<T *>(p.y) + (size_t)(b * S + t) * p.ldy + h * FT_HD;
 #pragma unroll 1
@@ -224,6 +238,21 @@ attn_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       uint32_t r[32];
       tc_ld32(tmem_o + lane_addr + (uint32_t)c0, r);
       if (t < S) {
+        if (p.gate_mode == 2) {  // a gate per output element: 64 bytes of logits per 32 columns (ldg % 8 == 0, 16-byte base)
+          const uint4 *g4 = reinterpret_cast<const uint4 *>(gsrc + h * FT_HD + c0);
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            const uint4 gv = g4[q];
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              const float2 gl = DT<T>::unpack2(gw[e]);
+              const int i = 8 * q + 2 * e;
+              r[i] = __float_as_uint(__uint_as_float(r[i]) / (1.0f + expf(-gl.x)));
+              r[i + 1] = __float_as_uint(__uint_as_float(r[i + 1]) / (1.0f + expf(-gl.y)));
+            }
+          }
+        }
         uint32_t o[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) o[i] = pack2x<T>(__uint_as_float(r[2 * i]) * inv, __uint_as_float(r[2 * i + 1]) * inv);

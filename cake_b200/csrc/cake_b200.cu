@@ -1202,11 +1202,12 @@ static int make_tmap(CUtensorMap *m, const void *ptr, uint64_t rows, uint64_t K,
 // [slabs][rows][cols] tensor of D with a slab stride of slab_rows rows -> 3-D map, (64 x box_rows x 1) box, 128-byte swizzle.
 // `rows` is the VISIBLE extent: the TMA unit zero-fills rows past it (query rows >= S, keys >= the attended length), so a
 // tile never carries a neighbouring slab's rows or uninitialised cache memory into an MMA.
+// slab_stride_elems > 0: the slabs lie that many elements apart (heads side by side inside a row) instead of slab_rows rows.
 static int make_tmap3(CUtensorMap *m, const void *ptr, uint64_t cols, uint64_t row_stride_elems, uint64_t rows, uint64_t slab_rows,
-                      uint64_t slabs, int dtype, uint32_t box_rows) {
+                      uint64_t slabs, int dtype, uint32_t box_rows, uint64_t slab_stride_elems = 0) {
   RC(tmap_init());
   const cuuint64_t gdim[3] = {cols, rows, slabs};
-  const cuuint64_t gstride[2] = {row_stride_elems * 2, slab_rows * row_stride_elems * 2};
+  const cuuint64_t gstride[2] = {row_stride_elems * 2, (slab_stride_elems ? slab_stride_elems : slab_rows * row_stride_elems) * 2};
   const cuuint32_t box[3] = {64u, box_rows, 1u};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = g_encode_tiled(m, dtype == CAKE_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
@@ -1540,6 +1541,28 @@ template <typename T> static int listed_attention_tc(cake_b200_ctx *c, const Win
   return launch_pdl(c, attn_window_tc_kernel<T>, gt, dim3(FT_THREADS), (size_t)FT_SMEM_BYTES, mq, mk, mk, wa, fa_tau * 1.4426950408889634f);
 }
 template <> int listed_attention_tc<float>(cake_b200_ctx *, const WinAttn &, bool *done) { *done = false; return CAKE_B200_OK; }
+// attn_window_tc_kernel with its optional parts (kept first keys, sink, a gate buffer, buffers that start at key0).
+// kv_row: 0 = kc / vc are caches [B, n_kv, cap, 128]; > 0 = they hold rows of that many elements with the heads side by side
+// (one batch row; rows = positions key0 ..).
+template <typename T> static int window_attention_tc(cake_b200_ctx *c, const WinAttn &wa, int kv_row, uint64_t *lc) {
+  static const float fa_tau = []() { const char *e = getenv("CAKE_B200_FA_TAU"); return e ? (float)atof(e) : 5.545f; }();
+  if (wa.hd != FT_HD || wa.ldy % 8 != 0 || wa.ld % 8 != 0 || (kv_row && wa.B != 1) || (wa.gate_mode == 2 && (wa.ldg % 8 != 0 || ((uintptr_t)wa.gate & 15) != 0)))
+    return fail(CAKE_B200_EINVAL, "window attention on the tensor cores: shapes not supported");
+  CUtensorMap mq, mk, mv;
+  const uint64_t vis = (uint64_t)(wa.pos0 + wa.S - wa.key0);
+  RC(make_tmap3(&mq, wa.qkg, (uint64_t)wa.ld, (uint64_t)wa.ld, (uint64_t)wa.S, (uint64_t)wa.S, (uint64_t)wa.B, c->cfg.dtype, FT_BM));
+  if (kv_row) {
+    RC(make_tmap3(&mk, wa.kc, (uint64_t)FT_HD, (uint64_t)kv_row, vis, 0, (uint64_t)wa.n_kv, c->cfg.dtype, FT_BN, (uint64_t)FT_HD));
+    RC(make_tmap3(&mv, wa.vc, (uint64_t)FT_HD, (uint64_t)kv_row, vis, 0, (uint64_t)wa.n_kv, c->cfg.dtype, FT_BN, (uint64_t)FT_HD));
+  } else {
+    RC(make_tmap3(&mk, wa.kc, (uint64_t)FT_HD, (uint64_t)FT_HD, vis, (uint64_t)wa.cap, (uint64_t)wa.B * wa.n_kv, c->cfg.dtype, FT_BN));
+    RC(make_tmap3(&mv, wa.vc, (uint64_t)FT_HD, (uint64_t)FT_HD, vis, (uint64_t)wa.cap, (uint64_t)wa.B * wa.n_kv, c->cfg.dtype, FT_BN));
+  }
+  dim3 gt((wa.S + FT_BM - 1) / FT_BM, wa.heads, wa.B);
+  (void)lc;  // launch_pdl counts
+  return launch_pdl(c, attn_window_tc_kernel<T>, gt, dim3(FT_THREADS), (size_t)FT_SMEM_BYTES, mq, mk, mv, wa, fa_tau * 1.4426950408889634f);
+}
+template <> int window_attention_tc<float>(cake_b200_ctx *, const WinAttn &, int, uint64_t *) { return CAKE_B200_EINVAL; }
 // steps of a few tokens in 16-bit D with 16-byte rows: eight lanes per key (attn_window_decode_vec_kernel)
 template <typename T> static int listed_attention_vec(cake_b200_ctx *c, const WinAttn &wa, bool *done) {
   *done = false;
@@ -2141,12 +2164,25 @@ static int cache_ensure_ext(cake_b200_cache *k, int layer, const cake_b200_block
 
 // scratch of one mixer of an ext block
 struct SubScratch {
-  void *att, *conv, *qh, *pw, *oh, *cq, *qa, *lat;
+  void *att, *conv, *qh, *pw, *oh, *cq, *qa, *lat, *kx, *vx;
   float *o32, *qn, *kn, *f1, *f2, *f3, *part, *y, *scores, *stats;
   int nsplit, tc_tok;
 };
 constexpr int TALK_SPLIT_MAX = 64;
 constexpr int WIN_SPLIT_MAX = 32;
+// Sink attention and windowed latent attention of a portion on attn_window_tc_kernel: 16-bit D, key and value size 128, a step
+// of at least half a query tile; the latent kind expands keys and values of all heads with two products per batch row first.
+constexpr int WIN_TC_MIN_ROWS = 64;
+static bool window_on_tc(const cake_b200_ctx *c, const cake_b200_block *b, int S) {
+  static const bool off = []() {
+    const char *e = getenv("CAKE_B200_NO_TC"), *f = getenv("CAKE_B200_FA");
+    return (e && e[0] == '1') || (f && !strcmp(f, "mma"));
+  }();
+  const cake_b200_mixer_spec &sp = b->ms;
+  if (off || c->cfg.dtype == CAKE_B200_F32 || S < WIN_TC_MIN_ROWS || sp.dim != FT_HD || sp.vdim != FT_HD || b->n_in_pad % 8 != 0) return false;
+  if (sp.kind == CAKE_B200_MIX_SINK_ATTENTION) return b->pc[3] < 0 || b->pc[3] % 8 == 0;
+  return sp.kind == CAKE_B200_MIX_LATENT_WINDOW && sp.kv_rank % TC_BK == 0;
+}
 template <typename Take> static SubScratch sub_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, int S, int n_keys, Take &&take) {
   SubScratch s{};
   const cake_b200_mixer_spec &sp = b->ms;
@@ -2159,8 +2195,14 @@ template <typename Take> static SubScratch sub_scratch(const cake_b200_ctx *c, c
     s.qh = take(M * sp.heads * sp.dim * es);  // rotated unit queries / the expanded queries
     if (latent) {
       s.cq = take(M * sp.q_rank * es);
-      s.qa = take(M * sp.heads * sp.kv_rank * es);
-      s.lat = take(M * sp.heads * sp.kv_rank * es);
+      if (window_on_tc(c, b, S)) {  // keys and values of every head for the rows one batch row's step sees
+        const size_t nk = sp.window > 0 ? std::min<size_t>(n_keys, (size_t)S + sp.window - 1) : (size_t)n_keys;
+        s.kx = take(nk * sp.heads * sp.dim * es);
+        s.vx = take(nk * sp.heads * sp.vdim * es);
+      } else {
+        s.qa = take(M * sp.heads * sp.kv_rank * es);
+        s.lat = take(M * sp.heads * sp.kv_rank * es);
+      }
     }
     // steps of a few rows over many visible keys: split the keys so that the step fills the chip
     const int vis = std::min(n_keys, sp.window > 0 ? sp.window + sp.keep_first : n_keys);
@@ -2215,7 +2257,7 @@ template <typename Take> static MoeScratch moe_scratch(const cake_b200_ctx *c, c
 template <typename T>
 static int enqueue_routed_ff(cake_b200_ctx *c, const cake_b200_block *b, const MoeScratch &w, const void *h, const float *x, float *out, int M, uint64_t *lc);
 struct ExtScratch {
-  void *h, *proj, *act;
+  void *h, *proj, *act, *side;
   float *h32;
   SubScratch a, b;
   MoeScratch moe;
@@ -2236,6 +2278,7 @@ static ExtScratch ext_scratch(const cake_b200_ctx *c, const cake_b200_block *b, 
   s.a = sub_scratch(c, b, M, S, n_keys, take);
   if (b->side) s.b = sub_scratch(c, b->side, M, S, n_keys, take);
   if (b->ms.dense_ff > 0) s.act = take(M * (size_t)b->ms.dense_ff * es);
+  if (b->ms.side_dim > 0) s.side = take(M * (size_t)b->ms.side_dim * es);
   s.moe = moe_scratch(c, b, M, take);
   s.total = off;
   return s;
@@ -2313,7 +2356,12 @@ static int run_sub_mixer(cake_b200_ctx *c, const cake_b200_block *b, cake_b200_c
     MX(mx::qk_prep(st, dt, qp, lc));
     mx::WindowAttn wa{w.qh, sp.heads * sp.dim, kc->k[slot], kc->v[slot], b->pc[3] >= 0 ? proj + b->pc[3] : nullptr, ldp, 0, b->m_sink, w.att, inner,
                       B, S, sp.heads, G, sp.dim, sp.vdim, kc->cap, pos0, sp.window, sp.keep_first, sp.scale, w.part, w.nsplit};
-    if (mx::window_attention_tiled_ok(dt, wa)) MX(mx::window_attention_tiled(st, dt, wa, lc));
+    if (window_on_tc(c, b, S)) {
+      const void *gate = b->pc[3] >= 0 ? proj + b->pc[3] : nullptr;
+      WinAttn ta{w.qh, kc->k[slot], kc->v[slot], nullptr, nullptr, w.att, B, S, sp.heads, G, FT_HD, kc->cap, pos0, sp.heads * FT_HD, inner, -1, sp.window,
+                 sp.scale, 0.f, sp.keep_first, 0, b->m_sink, gate, gate ? 2 : 0, ldp};
+      RC(window_attention_tc<T>(c, ta, 0, lc));
+    } else if (mx::window_attention_tiled_ok(dt, wa)) MX(mx::window_attention_tiled(st, dt, wa, lc));
     else MX(mx::window_attention(st, dt, wa, lc));
   } else if (sp.kind == CAKE_B200_MIX_LATENT_WINDOW) {
     // both latents are normed (the key / value latent straight into the cache), the query latent is expanded and taken through
@@ -2328,6 +2376,21 @@ static int run_sub_mixer(cake_b200_ctx *c, const cake_b200_block *b, cake_b200_c
     else {
       RowsGemm gq{w.cq, b->m_uq, nullptr, w.qh, M, sp.heads * sp.dim, sp.q_rank, sp.q_rank, sp.heads * sp.dim, 0, 0.f};
       RC((gemm_rows_T<T, RE_STORE>(c, gq)));
+    }
+    if (window_on_tc(c, b, S)) {
+      // a portion: k = uk c and v = uv c of all heads for the rows the step sees (two products per batch row), then the
+      // windowed attention over them with a gate per head
+      const int key0 = sp.window > 0 ? std::max(0, pos0 - sp.window + 1) : 0, nk = pos0 + S - key0, qw = sp.heads * FT_HD;
+      for (int bb = 0; bb < B; bb++) {
+        const T *rows = (const T *)kc->k[slot] + ((size_t)bb * kc->cap + key0) * R;
+        RC((listed_gemm_tc<T, TCE_PLAIN>(c, rows, b->m_uk, nullptr, w.kx, nk, qw, R, 0, 0)));
+        RC((listed_gemm_tc<T, TCE_PLAIN>(c, rows, b->m_uv, nullptr, w.vx, nk, qw, R, 0, 0)));
+        const void *gate = b->pc[3] >= 0 ? proj + (size_t)bb * S * ldp + b->pc[3] : nullptr;
+        WinAttn ta{(const T *)w.qh + (size_t)bb * S * qw, w.kx, w.vx, nullptr, nullptr, (T *)w.att + (size_t)bb * S * inner, 1, S, sp.heads, sp.heads, FT_HD, nk,
+                   pos0, qw, inner, -1, sp.window, sp.scale, 0.f, 0, key0, nullptr, gate, gate ? 1 : 0, ldp};
+        RC(window_attention_tc<T>(c, ta, qw, lc));
+      }
+      return with_out ? gemm_f32_out<T>(c, w.att, b->wo, w.y, M, H, inner) : CAKE_B200_OK;
     }
     mx::HeadGemm ga{w.qh, b->m_uk, w.qa, M, R, sp.dim, sp.heads, sp.dim, (long)sp.dim * R, R, sp.heads * sp.dim, R, sp.heads * R, 1};
     MX(mx::head_gemm(st, dt, ga, lc));
@@ -2449,8 +2512,23 @@ static int enqueue_ext_layer(cake_b200_ctx *c, const cake_b200_block *b, int l, 
   if (sp.side_dim > 0) {
     if (!c->side_tab || sp.side_col + sp.side_dim > c->side_cols) return fail(CAKE_B200_ESTATE, "layer %d: the token input needs columns %d..%d of the side table (%d loaded)", b->layer, sp.side_col, sp.side_col + sp.side_dim, c->side_cols);
     if (c->d_ids_n != (size_t)M) return fail(CAKE_B200_ESTATE, "layer %d: the token input needs the ids of this step (%zu embedded, %d rows)", b->layer, c->d_ids_n, M);
-    mx::TokenSide ts{x_out, x_out, c->d_ids, c->side_tab, c->side_cols, sp.side_col, b->sd_gate, b->sd_proj, b->sd_norm, M, H, sp.side_dim, eps};
-    MX(mx::token_side(st, dt, ts, lc));
+    // g = gelu(G x) * e and y = P g as two products with the gate between them; x += rms(y) * w is a merge with a post norm
+    const int sd = sp.side_dim;
+    const void *xa = x_out;  // D = float: the stream is the operand as it stands
+    if (dt != CAKE_B200_F32) {
+      MX(mx::rows_to_d(st, dt, x_out, w.h, (size_t)M * H, lc));
+      xa = w.h;
+    }
+    if (listed_tc<T>(c, M, sd, H)) RC((listed_gemm_tc<T, TCE_PLAIN>(c, xa, b->sd_gate, nullptr, w.side, M, sd, H, 0, 0)));
+    else {
+      RowsGemm gg{xa, b->sd_gate, nullptr, w.side, M, sd, H, H, sd, 0, 0.f};
+      RC((gemm_rows_T<T, RE_STORE>(c, gg)));
+    }
+    mx::SideGate sg{w.side, sd, c->d_ids, c->side_tab, c->side_cols, sp.side_col, M, sd};
+    MX(mx::side_gate(st, dt, sg, lc));
+    RC(gemm_f32_out<T>(c, w.side, b->sd_proj, w.a.y, M, H, sd));
+    mx::BranchMerge sm{w.a.y, nullptr, nullptr, nullptr, nullptr, nullptr, b->sd_norm, 0.f, x_out, x_out, M, H, eps};
+    MX(mx::branch_merge(st, dt, sm, lc));
   }
   return CAKE_B200_OK;
 }

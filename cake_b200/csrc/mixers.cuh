@@ -402,17 +402,18 @@ bool window_attention_tiled_ok(int dtype, const WindowAttn &);
 int window_attention_tiled(cudaStream_t, int dtype, const WindowAttn &, uint64_t *launches);
 
 // ---- per-layer token input: x += rms(P (gelu_tanh(G x) * e)) * w,  e = table[id, col .. col + dim) ----------------------------
-struct TokenSide {
-  const float *x;        // [M, W] fp32
-  float *x_out;          // may alias x
+// The two products run on the GEMMs of the caller; these are the steps around them: the stream's rows rounded to D (the first
+// product's operand in 16-bit D), and g <- gelu_tanh(g) * e in place on the first product's result.
+int rows_to_d(cudaStream_t, int dtype, const float *x, void *out, size_t n, uint64_t *launches);
+struct SideGate {
+  void *g;               // [M, ld] D, in place
+  int ld;
   const uint32_t *ids;   // [M]
   const void *table;     // [vocab, table_ld] D
   int table_ld, col;
-  const void *gate, *proj, *norm;   // [dim, W], [W, dim], [W] D
-  int M, W, dim;
-  float eps;
+  int M, dim;
 };
-int token_side(cudaStream_t, int dtype, const TokenSide &, uint64_t *launches);
+int side_gate(cudaStream_t, int dtype, const SideGate &, uint64_t *launches);
 
 // ---- out[m] = [x[m] | x0[m]] in D  (the operand of a projection of the stream and the embedding output back into the stream) --
 int concat_rows(cudaStream_t, int dtype, const float *x, const float *x0, void *out, int M, int W, uint64_t *launches);

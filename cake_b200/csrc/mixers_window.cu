@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
+#include <algorithm>
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -499,48 +500,38 @@ int window_attention_tiled(cudaStream_t st, int dtype, const WindowAttn &p, uint
 
 // ---------------------------------------------------------------------------------------------- per-layer token input
 template <typename T>
-__global__ void __launch_bounds__(256) token_side_kernel(const TokenSide p) {
-  extern __shared__ float sm[];  // g [dim], y [W]
-  __shared__ float red[8];
-  float *gs = sm, *ys = sm + p.dim;
-  const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const float *x = p.x + (size_t)m * p.W;
-  const T *e = reinterpret_cast<const T *>(p.table) + (size_t)p.ids[m] * p.table_ld + p.col;
-  const T *G = reinterpret_cast<const T *>(p.gate), *P = reinterpret_cast<const T *>(p.proj), *nw = reinterpret_cast<const T *>(p.norm);
-  for (int j = warp; j < p.dim; j += 8) {
-    const T *gr = G + (size_t)j * p.W;
-    float d = 0.f;
-    for (int i = lane; i < p.W; i += 32) d = fmaf(DT<T>::to_f(gr[i]), x[i], d);
-    d = warp_sum(d);
-    if (lane == 0) gs[j] = 0.5f * d * (1.0f + tanhf(0.7978845608028654f * (d + 0.044715f * d * d * d))) * DT<T>::to_f(e[j]);
+__global__ void __launch_bounds__(256) rows_to_d_kernel(const float *__restrict__ x, T *__restrict__ out, size_t n) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t n4 = ((((uintptr_t)x | (uintptr_t)out) & 15) == 0) ? n / 4 : 0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 v = reinterpret_cast<const float4 *>(x)[i];
+    T *o = out + 4 * i;
+    o[0] = DT<T>::from_f(v.x); o[1] = DT<T>::from_f(v.y); o[2] = DT<T>::from_f(v.z); o[3] = DT<T>::from_f(v.w);
   }
-  __syncthreads();
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < p.W; i += blockDim.x) {
-    const T *pr = P + (size_t)i * p.dim;
-    float y = 0.f;
-    for (int j = 0; j < p.dim; j++) y = fmaf(DT<T>::to_f(pr[j]), gs[j], y);
-    ys[i] = y;
-    ss = fmaf(y, y, ss);
-  }
-  ss = warp_sum(ss);
-  if (lane == 0) red[warp] = ss;
-  __syncthreads();
-  float tot = 0.f;
-  for (int w = 0; w < 8; w++) tot += red[w];
-  const float inv = 1.0f / sqrtf(tot / (float)p.W + p.eps);
-  for (int i = threadIdx.x; i < p.W; i += blockDim.x) p.x_out[(size_t)m * p.W + i] = x[i] + ys[i] * inv * DT<T>::to_f(nw[i]);
+  for (size_t i = 4 * n4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = DT<T>::from_f(x[i]);
 }
-int token_side(cudaStream_t st, int dtype, const TokenSide &p, uint64_t *launches) {
-  const size_t smem = (size_t)(p.dim + p.W) * sizeof(float);
-  if (p.M < 1 || p.W < 1 || p.dim < 1 || smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-  MX_DISPATCH(dtype, {
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(token_side_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-    }
-    token_side_kernel<T><<<p.M, 256, smem, st>>>(p);
-  });
+int rows_to_d(cudaStream_t st, int dtype, const float *x, void *out, size_t n, uint64_t *launches) {
+  if (!x || !out || n < 1) return (int)cudaErrorInvalidValue;
+  const unsigned grid = (unsigned)std::min<size_t>((n / 4 + 255) / 256 + 1, 148 * 16);
+  MX_DISPATCH(dtype, (rows_to_d_kernel<T><<<grid, 256, 0, st>>>(x, reinterpret_cast<T *>(out), n)));
+  MX_DONE(1);
+}
+template <typename T>
+__global__ void __launch_bounds__(256) side_gate_kernel(const SideGate p) {
+  const size_t total = (size_t)p.M * p.dim;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = i / p.dim;
+    const int j = (int)(i % p.dim);
+    T *g = reinterpret_cast<T *>(p.g) + m * p.ld + j;
+    const float d = DT<T>::to_f(*g);
+    const float e = DT<T>::to_f(reinterpret_cast<const T *>(p.table)[(size_t)p.ids[m] * p.table_ld + p.col + j]);
+    *g = DT<T>::from_f(0.5f * d * (1.0f + tanhf(0.7978845608028654f * (d + 0.044715f * d * d * d))) * e);
+  }
+}
+int side_gate(cudaStream_t st, int dtype, const SideGate &p, uint64_t *launches) {
+  if (p.M < 1 || p.dim < 1 || !p.g || !p.ids || !p.table) return (int)cudaErrorInvalidValue;
+  const unsigned grid = (unsigned)std::min<size_t>(((size_t)p.M * p.dim + 255) / 256, 148 * 16);
+  MX_DISPATCH(dtype, (side_gate_kernel<T><<<grid, 256, 0, st>>>(p)));
   MX_DONE(1);
 }
 

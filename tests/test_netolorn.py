@@ -90,11 +90,11 @@ def plain(cfg, sd, toks, streams=None, d=None):
     return P.forward(toks, wt, d or cfg.to_hf(), torch.float32, streams).numpy()
 
 
-def plain_with_rounded_products(cfg, sd, toks):
-    """The plain model with the input and the result of every matrix product rounded to bfloat16: how far 16-bit rounding alone
+def plain_with_rounded_products(cfg, sd, toks, to=torch.bfloat16):
+    """The plain model with the input and the result of every matrix product rounded to 16 bits: how far that rounding alone
     moves the logits of a configuration (a router's close call, a sharp softmax), which is the bar a 16-bit run is held to."""
     exact = P.lin
-    P.lin = lambda W, x, b=None: exact(W, x.bfloat16().float(), b).bfloat16().float()
+    P.lin = lambda W, x, b=None: exact(W, x.to(to).float(), b).to(to).float()
     try:
         return plain(cfg, sd, toks)
     finally:
@@ -430,6 +430,46 @@ def test_window_edges_kept_tokens_and_the_sink(kind):
         close(rb.run("c", toks, cuts=[30, 1]), wb, "bf16", "decoded, bf16")
     finally:
         rb.close()
+
+
+@pytest.mark.gpu
+def test_key_size_128_portions_on_the_tensor_core_attention():
+    """Key and value size 128 in 16-bit D: portions of 64 rows and more take the tensor-core attention (kept first keys ahead of the
+    window's tiles, the sink in the denominator, a gate per element; the latent kind with keys and values expanded for the rows a
+    step sees), shorter ones the other kernels.  Flat scores in f16, where rounding is small: a window or a kept range that is one
+    off, or a missing sink, moves the plain model's logits by several bars at most positions."""
+    layers = [sharp(attn(heads=4, kv_heads=2, dim=128, vdim=128, size=70, keep=5, rot=64, mlp=None), 0.2),
+              sharp(latent(heads=2, dim=128, vdim=128, q_rank=64, kv_rank=64, size=90, mlp=None), 0.05),
+              sharp(attn(heads=2, kv_heads=2, dim=128, vdim=128, size=0, keep=0, rot=32, scaling=None, mlp=dense(128)), 0.2),
+              sharp(latent(heads=2, dim=128, vdim=128, q_rank=64, kv_rank=128, size=0, mlp=None), 0.05)]
+    cfg = make_config(layers, width=128, vocab=96, side=0)
+    sd = make_netolorn_checkpoint(cfg, "f16", seed=47)
+    toks = tokens(400, cfg.vocab_size, seed=13)
+    want = plain(cfg, sd, toks)
+    bar = max(4 * float(np.quantile(errors(plain_with_rounded_products(cfg, sd, toks, torch.float16), want), 0.95)), 4e-3)
+
+    def mask(layer, which, dl):
+        def edit(d):
+            d["layers"][layer]["mixer"]["mask"][which] += dl
+        return edit
+    faults = {"window + 1": mask(0, "size", 1), "window - 1": mask(0, "size", -1), "kept + 1": mask(0, "keep_first", 1), "kept - 1": mask(0, "keep_first", -1),
+              "latent window + 1": mask(1, "size", 1), "latent window - 1": mask(1, "size", -1)}
+    for what, edit in faults.items():
+        e = errors(plain(cfg, sd, toks, d=faulty(cfg, edit))[200:], want[200:])
+        assert np.quantile(e, 0.5) > 2 * bar, f"{what} would not show: {np.quantile(e, 0.5):.3g} against {bar:.3g}"
+    nosink = dict(sd)
+    nosink["l0.mix.sink"] = torch.full_like(sd["l0.mix.sink"], -60.0)
+    assert np.quantile(errors(plain(cfg, nosink, toks), want), 0.5) > 2 * bar
+    r = Runner(cfg, sd, "f16")
+    try:
+        whole = r.run("w", toks)
+        close(whole, want, "f16", "whole", bar)
+        for cuts in ([200, 130, 70], [64, 65, 128, 143], [37], [150, 1, 1, 1, 100, 2, 145]):
+            got = r.run("c", toks, cuts=cuts)
+            close(got, want, "f16", f"portions {cuts}", bar)
+            close(got, whole, "f16", f"portions {cuts} against whole", bar)
+    finally:
+        r.close()
 
 
 @pytest.mark.gpu
