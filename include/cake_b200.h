@@ -222,7 +222,8 @@ int cake_b200_block_load_spec(cake_b200_ctx *, int layer_idx, const cake_b200_la
  *                            (g [heads * vdim, hidden]; NULL = none); then o.  K and V rows live in the cache.
  *   CAKE_B200_MIX_LATENT_WINDOW  latent attention without positions: c_q = rms(dq h) * dq_norm ([q_rank]), q = uq c_q ([heads * dim,
  *                            q_rank]); c = rms(dkv h) * dkv_norm ([kv_rank]) is the only cached row; per head k = uk c, v = uv c
- *                            (computed in the absorbed form: the query goes through uk, the weighted latent through uv);
+ *                            (steps of a few rows in the absorbed form: the query goes through uk, the weighted latent through
+ *                            uv; portions with key and value size 128 in 16-bit D expand k and v for the rows the step sees);
  *                            score = (q . k) * scale over the window (as above, keep_first included); head h's output is
  *                            multiplied by sigmoid(g h)_h (g [heads, hidden]; NULL = none); then o.
  * Block structure switches (all 0 / NULL for the plain pre-norm block above):

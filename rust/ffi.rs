@@ -108,6 +108,7 @@ extern "C" {
         tensors: *const cake_b200_mixer_tensors, out: *mut *mut cake_b200_block) -> c_int;
     pub fn cake_b200_stream_inject(ctx: *mut cake_b200_ctx, x_dev: *mut f32, x0_dev: *const f32, vec: *const c_void, slot: c_int,
         rows: c_int) -> c_int;
+    pub fn cake_b200_stream_project(ctx: *mut cake_b200_ctx, x_dev: *mut f32, x0_dev: *const f32, w: *const c_void, rows: c_int) -> c_int;
     pub fn cake_b200_head_load_tables(ctx: *mut cake_b200_ctx, tables: *const cake_b200_embed_tables) -> c_int;
     pub fn cake_b200_embed_at(ctx: *mut cake_b200_ctx, cache: *mut cake_b200_cache, ids_host: *const u32, batch: c_int, seq: c_int,
         index_pos: c_int, x_dev: *mut c_void) -> c_int;
@@ -123,6 +124,11 @@ pub struct cake_b200_embed_tables {
     pub pos: *const c_void,
     pub pos_rows: c_int,
     pub final_norm_offset: f32,
+    pub side: *const c_void,
+    pub side_cols: c_int,
+    pub final_norm_kind: c_int,
+    pub final_alpha: f32,
+    pub final_bias: *const c_void,
 }
 
 /// `cake_b200_rotary_spec`, `cake_b200_moe_spec`, `cake_b200_mixer_spec`, `cake_b200_mixer_tensors` (include/cake_b200.h): a
@@ -145,6 +151,9 @@ pub struct cake_b200_moe_spec {
     pub ff: c_int,
     pub shared_ff: c_int,
     pub act: c_int,
+    pub limit: f32,
+    pub shared_limit: f32,
+    pub logit_bias: c_int,
 }
 #[repr(C)]
 pub struct cake_b200_mixer_spec {
@@ -173,6 +182,15 @@ pub struct cake_b200_mixer_spec {
     pub dense_act: c_int,
     pub dense_limit: f32,
     pub side: *const cake_b200_mixer_spec,
+    // sink attention / windowed latent attention, squashing norms, the per-layer token input
+    pub window: c_int,
+    pub keep_first: c_int,
+    pub qk_unit: c_int,
+    pub q_rank: c_int,
+    pub norm_kind: c_int,
+    pub norm_alpha: [f32; 4],
+    pub side_dim: c_int,
+    pub side_col: c_int,
 }
 #[repr(C)]
 pub struct cake_b200_mixer_tensors {
@@ -226,6 +244,17 @@ pub struct cake_b200_mixer_tensors {
     pub ff_down: *const c_void,
     pub branch_norm: *const c_void,
     pub side: *const cake_b200_mixer_tensors,
+    pub sink: *const c_void,
+    pub dq: *const c_void,
+    pub dq_norm: *const c_void,
+    pub uq: *const c_void,
+    pub norm1_b: *const c_void,
+    pub post1_b: *const c_void,
+    pub norm2_b: *const c_void,
+    pub post2_b: *const c_void,
+    pub side_gate: *const c_void,
+    pub side_proj: *const c_void,
+    pub side_norm: *const c_void,
 }
 
 /// `cake_b200_block_variant` (include/cake_b200.h): norm placement and per-layer attention mode of the OLMo2 / Gemma3 /
