@@ -468,6 +468,20 @@ def test_key_size_128_portions_on_the_tensor_core_attention():
             got = r.run("c", toks, cuts=cuts)
             close(got, want, "f16", f"portions {cuts}", bar)
             close(got, whole, "f16", f"portions {cuts} against whole", bar)
+        # two unequal batch rows in one call, in two portions (the second starts inside every window)
+        from cake_b200.model import Cache
+        rows = [toks[:300], tokens(300, cfg.vocab_size, seed=14)]
+        wants = [want[:300], plain(cfg, sd, rows[1])]
+        r.ctx.cache = Cache(r.ctx, 2, 320)
+        got, at = [], 0
+        for n in (200, 100):
+            lg = r.model.forward(np.array([t[at:at + n] for t in rows], dtype=np.uint32), at, want=list(range(2 * n)))
+            r.ctx.sync()
+            got.append(lg.cpu().numpy().reshape(2, n, -1))
+            at += n
+        got = np.concatenate(got, 1)
+        for i in range(2):
+            close(got[i], wants[i], "f16", f"batch row {i}", bar)
     finally:
         r.close()
 
