@@ -106,7 +106,7 @@ __device__ __forceinline__ float rotated_entry(const T *v, int i, int dims, cons
   return DT<T>::to_f(v[i]) * cs[i - half] + DT<T>::to_f(v[i - half]) * sn[i - half];
 }
 template <typename T>
-__global__ void __launch_bounds__(128) qk_prep_kernel(const QkPrep p) {
+__global__ void __launch_bounds__(256) qk_prep_kernel(const QkPrep p) {
   const int m = blockIdx.x, b = m / p.S, t = m % p.S, pos = p.pos0 + t;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const T *row = reinterpret_cast<const T *>(p.proj) + (size_t)m * p.ld;
@@ -135,9 +135,102 @@ __global__ void __launch_bounds__(128) qk_prep_kernel(const QkPrep p) {
     reinterpret_cast<T *>(p.vc)[(((size_t)b * p.kv_heads + g) * p.cap + pos) * p.vdim + e] = row[p.v_col + i];
   }
 }
+// The same for 16-bit D with head size 32 E (E = 2, 4, 8): a lane owns E adjacent entries of a head, so a head is one vector load
+// (two in the rotated part: the entries and their partners half the rotated width away), one vector load of cos and of sin, one
+// vector store.  The rotated half-width is a multiple of E, columns and strides multiples of 8.
+template <int E> __device__ __forceinline__ void load_words(const void *src, uint32_t (&w)[E / 2]) {
+  if (E == 2) w[0] = *reinterpret_cast<const uint32_t *>(src);
+  else if (E == 4) { const uint2 t = *reinterpret_cast<const uint2 *>(src); w[0] = t.x; w[1] = t.y; }
+  else { const uint4 t = *reinterpret_cast<const uint4 *>(src); w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w; }
+}
+template <int E> __device__ __forceinline__ void load_floats(const float *src, float (&f)[E]) {
+  if (E == 2) { const float2 t = *reinterpret_cast<const float2 *>(src); f[0] = t.x; f[1] = t.y; }
+  else {
+#pragma unroll
+    for (int q = 0; q < E / 4; q++) {
+      const float4 t = reinterpret_cast<const float4 *>(src)[q];
+      f[4 * q] = t.x; f[4 * q + 1] = t.y; f[4 * q + 2] = t.z; f[4 * q + 3] = t.w;
+    }
+  }
+}
+template <typename T, int E>
+__global__ void __launch_bounds__(256) qk_prep_vec_kernel(const QkPrep p) {
+  const int m = blockIdx.x, b = m / p.S, t = m % p.S, pos = p.pos0 + t;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const T *row = reinterpret_cast<const T *>(p.proj) + (size_t)m * p.ld;
+  const int dims = p.cos_t ? p.rope_dims : 0, half = dims >> 1, i0 = lane * E;
+  const float *cs = p.cos_t ? p.cos_t + (size_t)pos * half : nullptr, *sn = p.sin_t ? p.sin_t + (size_t)pos * half : nullptr;
+  for (int hv = warp; hv < p.heads + p.kv_heads; hv += nw) {
+    const bool is_q = hv < p.heads;
+    const int g = hv - p.heads;
+    const T *v = is_q ? row + p.q_col + (size_t)hv * p.dim : row + p.k_col + (size_t)g * p.dim;
+    T *o = is_q ? reinterpret_cast<T *>(p.q_out) + ((size_t)m * p.heads + hv) * p.dim
+                : reinterpret_cast<T *>(p.kc) + (((size_t)b * p.kv_heads + g) * p.cap + pos) * p.dim;
+    uint32_t wa[E / 2];
+    load_words<E>(v + i0, wa);
+    float r[E];
+#pragma unroll
+    for (int q = 0; q < E / 2; q++) {
+      const float2 f = DT<T>::unpack2(wa[q]);
+      r[2 * q] = f.x;
+      r[2 * q + 1] = f.y;
+    }
+    if (i0 < dims) {
+      const bool lo = i0 < half;
+      uint32_t wb[E / 2];
+      load_words<E>(v + (lo ? i0 + half : i0 - half), wb);
+      float c[E], sfac[E];
+      load_floats<E>(cs + (lo ? i0 : i0 - half), c);
+      load_floats<E>(sn + (lo ? i0 : i0 - half), sfac);
+#pragma unroll
+      for (int q = 0; q < E / 2; q++) {
+        const float2 f = DT<T>::unpack2(wb[q]);
+        r[2 * q] = lo ? r[2 * q] * c[2 * q] - f.x * sfac[2 * q] : r[2 * q] * c[2 * q] + f.x * sfac[2 * q];
+        r[2 * q + 1] = lo ? r[2 * q + 1] * c[2 * q + 1] - f.y * sfac[2 * q + 1] : r[2 * q + 1] * c[2 * q + 1] + f.y * sfac[2 * q + 1];
+      }
+    }
+    float inv = 1.f;
+    if (p.unit_norm) {
+      float ss = 0.f;
+#pragma unroll
+      for (int q = 0; q < E; q++) ss = fmaf(r[q], r[q], ss);
+      ss = warp_sum(ss);
+      inv = 1.0f / sqrtf(ss / (float)p.dim + p.eps);
+    }
+    uint32_t wo[E / 2];
+#pragma unroll
+    for (int q = 0; q < E / 2; q++) wo[q] = pack2x<T>(r[2 * q] * inv, r[2 * q + 1] * inv);
+    if (E == 2) *reinterpret_cast<uint32_t *>(o + i0) = wo[0];
+    else if (E == 4) *reinterpret_cast<uint2 *>(o + i0) = make_uint2(wo[0], wo[1]);
+    else *reinterpret_cast<uint4 *>(o + i0) = make_uint4(wo[0], wo[E / 2 > 1 ? 1 : 0], wo[E / 2 > 2 ? 2 : 0], wo[E / 2 > 3 ? 3 : 0]);
+  }
+  const int vrow = p.kv_heads * p.vdim;  // values: 16-byte pieces (vdim, v_col multiples of 8)
+  for (int i = threadIdx.x * 8; i < vrow; i += blockDim.x * 8) {
+    const int g = i / p.vdim, e = i % p.vdim;
+    *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(p.vc) + (((size_t)b * p.kv_heads + g) * p.cap + pos) * p.vdim + e) =
+        *reinterpret_cast<const uint4 *>(row + p.v_col + i);
+  }
+}
+template <typename T> static bool qk_prep_vec(cudaStream_t st, const QkPrep &p) {
+  const int E = p.dim / 32, half = p.cos_t ? p.rope_dims / 2 : 0;
+  const bool ok = p.dim % 32 == 0 && (E == 2 || E == 4 || E == 8) && half % E == 0 && p.vdim % 8 == 0 && p.ld % 8 == 0 && p.q_col % 8 == 0 &&
+                  p.k_col % 8 == 0 && p.v_col % 8 == 0 &&
+                  (((uintptr_t)p.proj | (uintptr_t)p.q_out | (uintptr_t)p.kc | (uintptr_t)p.vc | (uintptr_t)p.cos_t | (uintptr_t)p.sin_t) & 15) == 0 &&
+                  (half * sizeof(float)) % 16 == 0;
+  if (!ok) return false;
+  const unsigned nt = (p.heads + p.kv_heads) > 4 ? 256 : 128;
+  if (E == 2) qk_prep_vec_kernel<T, 2><<<p.B * p.S, nt, 0, st>>>(p);
+  else if (E == 4) qk_prep_vec_kernel<T, 4><<<p.B * p.S, nt, 0, st>>>(p);
+  else qk_prep_vec_kernel<T, 8><<<p.B * p.S, nt, 0, st>>>(p);
+  return true;
+}
+template <> bool qk_prep_vec<float>(cudaStream_t, const QkPrep &) { return false; }
 int qk_prep(cudaStream_t st, int dtype, const QkPrep &p, uint64_t *launches) {
   if (p.B < 1 || p.S < 1 || p.heads < 1 || p.kv_heads < 1 || (p.cos_t && (p.rope_dims & 1 || p.rope_dims > p.dim))) return (int)cudaErrorInvalidValue;
-  MX_DISPATCH(dtype, (qk_prep_kernel<T><<<p.B * p.S, 128, 0, st>>>(p)));
+  bool done = false;
+  MX_DISPATCH(dtype, (done = qk_prep_vec<T>(st, p)));
+  if (done) MX_DONE(1);
+  MX_DISPATCH(dtype, (qk_prep_kernel<T><<<p.B * p.S, (p.heads + p.kv_heads) > 4 ? 256 : 128, 0, st>>>(p)));
   MX_DONE(1);
 }
 
